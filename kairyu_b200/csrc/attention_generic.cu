@@ -11,6 +11,13 @@
 // takes keys start+w, start+w+4, ... with an online softmax of its own, and the
 // four partial results are merged in warp order.  So a token's output does not
 // depend on what else is in the batch or how the prompt was cut.
+//
+// sinks (optional, one fp32 logit a query head): the softmax's denominator also holds exp(sink_h).
+// A sink is a term exp(sink) of the denominator alone, taken as stored; it is added once, after the warps' merge.
+//
+// v_dim (<= D): how many columns of a value row are used and written (out rows are Hq * v_dim wide).
+// Keys and values may be the same rows (a cache whose rows serve as both) with the values their
+// first v_dim columns.  Head h's output starts at column h * out_head_stride of its token's row.
 #include "common.cuh"
 
 #define ATT_WARPS 4
@@ -25,7 +32,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restr
                                const int* __restrict__ row_ids,
                                const int* __restrict__ block_table, int max_pages, int Hq, int Hkv,
                                int D, int page_size, int num_pages, float scale, int window,
-                               int* flag) {
+                               const float* __restrict__ sinks, int v_dim, int out_head_stride, int* flag) {
     pdl_wait();
     __shared__ float sm_acc[ATT_WARPS][ATT_MAX_D];
     __shared__ float sm_m[ATT_WARPS];
@@ -78,7 +85,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restr
 #pragma unroll
         for (int k = 0; k < ATT_MAX_K; ++k) {
             const int e = lane + 32 * k;
-            if (e < D) acc[k] = acc[k] * alpha + p * to_float(vp[e]);
+            if (e < v_dim) acc[k] = acc[k] * alpha + p * to_float(vp[e]);
         }
         m = m_new;
     }
@@ -86,7 +93,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restr
 #pragma unroll
     for (int k = 0; k < ATT_MAX_K; ++k) {
         const int e = lane + 32 * k;
-        if (e < D) sm_acc[warp][e] = acc[k];
+        if (e < v_dim) sm_acc[warp][e] = acc[k];
     }
     if (lane == 0) {
         sm_m[warp] = m;
@@ -97,6 +104,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restr
     float big = -INFINITY;
 #pragma unroll
     for (int w = 0; w < ATT_WARPS; ++w) big = fmaxf(big, sm_m[w]);
+    const float sink = sinks ? sinks[h] : -INFINITY;
+    big = fmaxf(big, sink);
     float weights[ATT_WARPS];
     float denom = 0.0f;
 #pragma unroll
@@ -104,8 +113,9 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restr
         weights[w] = sm_m[w] == -INFINITY ? 0.0f : expf(sm_m[w] - big);
         denom += sm_l[w] * weights[w];
     }
-    T* op = out + (size_t)t * out_stride + (size_t)h * D;
-    for (int e = threadIdx.x; e < D; e += blockDim.x) {
+    if (sinks) denom += expf(sink - big);
+    T* op = out + (size_t)t * out_stride + (size_t)h * out_head_stride;
+    for (int e = threadIdx.x; e < v_dim; e += blockDim.x) {
         float v = 0.0f;
 #pragma unroll
         for (int w = 0; w < ATT_WARPS; ++w) v += sm_acc[w][e] * weights[w];
@@ -118,21 +128,23 @@ KB_EXPORT int kb_paged_attention_generic(const void* q, int q_stride, void* out,
                                          const int* positions, const int* row_ids,
                                          const int* block_table, int max_pages, int T, int Hq,
                                          int Hkv, int D, int page_size, int num_pages, float scale,
-                                         int window, int* flag, cudaStream_t stream) {
+                                         int window, const float* sinks, int v_dim, int out_head_stride, int* flag,
+                                         cudaStream_t stream) {
     if (T == 0) return 0;
     if (!q || !out || !k_cache || !v_cache || !positions || !row_ids || !block_table) return KB_ERR_NULL;
     if (D < 1 || D > ATT_MAX_D) return KB_ERR_UNSUPPORTED_SIZE;
+    if (v_dim < 1 || v_dim > D || out_head_stride < v_dim) return KB_ERR_BAD_ARG;
     if (Hkv < 1 || Hq % Hkv != 0 || Hq > 65535) return KB_ERR_BAD_ARG;
     dim3 grid(T, Hq);
     if (is_bf16)
         kb_launch(paged_attention_generic_kernel<__nv_bfloat16>, dim3(grid), dim3(ATT_WARPS * 32), 0, stream, 
             (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
             (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, positions, row_ids,
-            block_table, max_pages, Hq, Hkv, D, page_size, num_pages, scale, window, flag);
+            block_table, max_pages, Hq, Hkv, D, page_size, num_pages, scale, window, sinks, v_dim, out_head_stride, flag);
     else
         kb_launch(paged_attention_generic_kernel<float>, dim3(grid), dim3(ATT_WARPS * 32), 0, stream, 
             (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_cache,
             (const float*)v_cache, positions, row_ids, block_table, max_pages, Hq, Hkv, D,
-            page_size, num_pages, scale, window, flag);
+            page_size, num_pages, scale, window, sinks, v_dim, out_head_stride, flag);
     return kb_launch_result();
 }

@@ -11,6 +11,9 @@
 //   s_m(i, j) = cap * tanh(q_m(i) . k_m(j) * scale / cap)      (cap <= 0: no cap)
 //   a_m(i) = sum_j softmax_j(s_m(i, j)) v(j)   over max(0, i + 1 - window) <= j <= i
 //   o = a_1 - lambda * a_2   (MAPS = 1: o = a_1);  head_norm: o <- o * rsqrt(mean(o^2) + eps) * out_scale
+//   sinks (optional, one fp32 logit a query head): every map's denominator also holds exp(sink_h); a sink
+//   is a term exp(sink) of the denominator alone, taken as stored (all zeros: "one added to the denominator")
+//   gate (optional, [tokens, Hq * DV], the activations' dtype): o <- o * sigmoid(gate), last of all
 //
 // Query head h reads key/value head h / (Hq / Hkv).  The order of every sum depends on the
 // query's position, the window and the sizes only: warp w of a block takes keys start + w,
@@ -31,7 +34,8 @@ diff_attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restri
                               const T* __restrict__ k_cache, const T* __restrict__ v_cache, const int* __restrict__ positions,
                               const int* __restrict__ row_ids, const int* __restrict__ block_table, int max_pages, int Hq,
                               int Hkv, int D, int DV, int page_size, int num_pages, float scale, float cap, int window,
-                              float lambda, int head_norm, float eps, float out_scale, int* flag) {
+                              float lambda, int head_norm, float eps, float out_scale, const float* __restrict__ sinks,
+                              const T* __restrict__ gate, int gate_stride, int* flag) {
     pdl_wait();
     __shared__ float sm_acc[DA_WARPS][MAPS][DA_MAX_D];
     __shared__ float sm_m[DA_WARPS][MAPS];
@@ -125,7 +129,9 @@ diff_attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restri
         float top = -INFINITY;
 #pragma unroll
         for (int w = 0; w < DA_WARPS; ++w) top = fmaxf(top, sm_m[w][m]);
-        denom[m] = 0.0f;
+        const float sink = sinks ? sinks[h] : -INFINITY;
+        top = fmaxf(top, sink);
+        denom[m] = sinks ? expf(sink - top) : 0.0f;
 #pragma unroll
         for (int w = 0; w < DA_WARPS; ++w) {
             weights[m][w] = sm_m[w][m] == -INFINITY ? 0.0f : expf(sm_m[w][m] - top);
@@ -157,7 +163,11 @@ diff_attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restri
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int e = threadIdx.x + i * DA_WARPS * 32;
-        if (e < DV) op[e] = from_float<T>(o[i] * factor);
+        if (e < DV) {
+            float v = o[i] * factor;
+            if (gate) v *= 1.0f / (1.0f + expf(-to_float(gate[(size_t)t * gate_stride + (size_t)h * DV + e])));
+            op[e] = from_float<T>(v);
+        }
     }
 }
 
@@ -165,7 +175,8 @@ KB_EXPORT int kb_diff_attention_generic(const void* q, int q_stride, void* out, 
                                         const void* v_cache, int is_bf16, const int* positions, const int* row_ids,
                                         const int* block_table, int max_pages, int T, int Hq, int Hkv, int maps, int D, int DV,
                                         int page_size, int num_pages, float scale, float cap, int window, float lambda,
-                                        int head_norm, float eps, float out_scale, int* flag, cudaStream_t stream) {
+                                        int head_norm, float eps, float out_scale, const float* sinks, const void* gate,
+                                        int gate_stride, int* flag, cudaStream_t stream) {
     if (T == 0) return 0;
     if (!q || !out || !k_cache || !v_cache || !positions || !row_ids || !block_table) return KB_ERR_NULL;
     if (D < 1 || D > DA_MAX_D || DV < 1 || DV > DA_MAX_D || maps < 1 || maps > 2) return KB_ERR_UNSUPPORTED_SIZE;
@@ -174,7 +185,7 @@ KB_EXPORT int kb_diff_attention_generic(const void* q, int q_stride, void* out, 
 #define LAUNCH(TT, M)                                                                                                            \
     kb_launch(diff_attention_generic_kernel<TT, M>, grid, dim3(DA_WARPS * 32), 0, stream, (const TT*)q, q_stride, (TT*)out,       \
               out_stride, (const TT*)k_cache, (const TT*)v_cache, positions, row_ids, block_table, max_pages, Hq, Hkv, D, DV,     \
-              page_size, num_pages, scale, cap, window, lambda, head_norm, eps, out_scale, flag)
+              page_size, num_pages, scale, cap, window, lambda, head_norm, eps, out_scale, sinks, (const TT*)gate, gate_stride, flag)
     if (is_bf16) {
         if (maps == 2) LAUNCH(__nv_bfloat16, 2); else LAUNCH(__nv_bfloat16, 1);
     } else {

@@ -9,6 +9,9 @@
 //                 the runs are cut into tiles of MOE_TM pairs: tile -> (expert, first place, pairs).
 //   moe_route_scores  per token: softmax over all outputs, a correction that steers the choice only, groups of
 //                 neighbours of which the best stay, the K best that stay; weights = score * scale.  32-bit.
+//                 With `sigmoid` the scores are s = sigmoid(logit), each output by itself, instead of the softmax.
+//   moe_scale_rows  out[i] = src[token of i] * scale[pair of i]: the experts' input rows for a mixture whose router
+//                 weight multiplies an expert's INPUT (the experts are not linear, so it cannot move to the output).
 //   moe_activation  y = a * sigmoid(alpha a) * (b + shift) with a = min(gate, limit), b = clamp(up, +-limit)
 //                 over rows [gate columns | up columns]: for the path whose products are a library's.
 //   moe_grouped   one block per (tile, 64 output columns): a [pairs, K] x [K, 64] product with the
@@ -22,7 +25,8 @@
 //                 together and whoever adds them (weighted by the router) does so in the order of k.
 //                 bfloat16 runs on mma.sync m16n8k16 with 32-bit accumulators, float32 on FMAs; the
 //                 sum over K runs in ascending order in both, whatever else the tile holds.
-//   moe_combine   out[t] = sum_k weight[t, k] * rows[at(t * K + k)]   (for callers that want plain rows); a pair whose
+//   moe_combine   out[t] = sum_k weight[t, k] * rows[at(t * K + k)]   (for callers that want plain rows; no weights: a
+//                 plain sum) + sigmoid(extra_gate[t]) * extra[t] when an always-on expert's rows are given; a pair whose
 //                 id is not below the number of experts with weights is an identity expert: its row is the token's own.
 //                 The grouped kernels skip such pairs' tiles.
 #include "common.cuh"
@@ -441,20 +445,49 @@ moe_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int* __res
 template <typename TR, typename TO>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const TR* __restrict__ rows, const float* __restrict__ weights, const int* __restrict__ at, int K, int H,
-                   TO* __restrict__ out, const int* __restrict__ ids, const TO* __restrict__ x, int real_experts) {
+                   TO* __restrict__ out, const int* __restrict__ ids, const TO* __restrict__ x, int real_experts,
+                   const TO* __restrict__ extra, const float* __restrict__ extra_gate, int gate_stride) {
     pdl_wait();
     const int t = blockIdx.x;
+    const float extra_weight = extra ? (extra_gate ? 1.0f / (1.0f + expf(-extra_gate[(size_t)t * gate_stride])) : 1.0f) : 0.0f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float v = 0.0f;
         for (int k = 0; k < K; ++k) {
             const size_t p = (size_t)t * K + k;
+            const float w = weights ? weights[p] : 1.0f;
             if (ids && ids[p] >= real_experts)  // an identity expert: its output is the token's own row
-                v += weights[p] * to_float(x[(size_t)t * H + i]);
+                v += w * to_float(x[(size_t)t * H + i]);
             else
-                v += weights[p] * to_float(rows[(at ? (size_t)at[p] : p) * H + i]);
+                v += w * to_float(rows[(at ? (size_t)at[p] : p) * H + i]);
         }
+        if (extra) v += extra_weight * to_float(extra[(size_t)t * H + i]);
         out[(size_t)t * H + i] = from_float<TO>(v);
     }
+}
+
+// out[i] = src[rows ? rows[i] : i / div] * scale[index ? index[i] : i], in 32-bit with one rounding at the store
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_scale_rows_kernel(const T* __restrict__ src, const int* __restrict__ rows, int div, const float* __restrict__ scale,
+                      const int* __restrict__ index, T* __restrict__ out, int H) {
+    pdl_wait();
+    const int i = blockIdx.x;
+    const T* from = src + (size_t)(rows ? rows[i] : i / div) * H;
+    const float w = scale[index ? index[i] : i];
+    for (int c = threadIdx.x; c < H; c += blockDim.x) out[(size_t)i * H + c] = from_float<T>(to_float(from[c]) * w);
+}
+
+KB_EXPORT int kb_moe_scale_rows(const void* src, int is_bf16, const int* rows, int div, const float* scale, const int* index, void* out,
+                                int R, int H, cudaStream_t stream) {
+    if (R == 0) return 0;
+    if (!src || !scale || !out) return KB_ERR_NULL;
+    if (H < 1 || (!rows && div < 1)) return KB_ERR_BAD_ARG;
+    if (is_bf16)
+        kb_launch(moe_scale_rows_kernel<__nv_bfloat16>, dim3(R), dim3(256), 0, stream, (const __nv_bfloat16*)src, rows, div, scale, index,
+                  (__nv_bfloat16*)out, H);
+    else
+        kb_launch(moe_scale_rows_kernel<float>, dim3(R), dim3(256), 0, stream, (const float*)src, rows, div, scale, index, (float*)out, H);
+    return kb_launch_result();
 }
 
 // Routing by scores: s = softmax(logits) over all n outputs; the choice runs on c = s + correction
@@ -465,7 +498,7 @@ moe_combine_kernel(const TR* __restrict__ rows, const float* __restrict__ weight
 template <typename TB>
 __global__ void __launch_bounds__(128)
 moe_route_scores_kernel(const float* __restrict__ logits, const TB* __restrict__ correction, int n, int K, int groups, int keep,
-                        float scale, int* __restrict__ ids, float* __restrict__ weights, int T) {
+                        float scale, int sigmoid, int stride, int* __restrict__ ids, float* __restrict__ weights, int T) {
     extern __shared__ float route_shared[];  // per warp: s[n], c[n], group values [groups]
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -474,17 +507,17 @@ moe_route_scores_kernel(const float* __restrict__ logits, const TB* __restrict__
     float* s = route_shared + (size_t)warp * (2 * n + groups);
     float* c = s + n;
     float* group_value = c + n;
-    const float* z = logits + (size_t)t * n;
+    const float* z = logits + (size_t)t * stride;  // a row may hold further columns behind the n router outputs
     float top = -INFINITY;
     for (int e = lane; e < n; e += 32) top = fmaxf(top, z[e]);
     top = warp_max(top);
     float sum = 0.0f;
     for (int e = lane; e < n; e += 32) {
-        const float p = expf(z[e] - top);
+        const float p = sigmoid ? 1.0f / (1.0f + expf(-z[e])) : expf(z[e] - top);
         s[e] = p;
         sum += p;
     }
-    sum = warp_sum(sum);
+    sum = sigmoid ? 1.0f : warp_sum(sum);
     for (int e = lane; e < n; e += 32) {
         s[e] = s[e] / sum;
         c[e] = s[e] + (correction ? to_float(correction[e]) : 0.0f);
@@ -541,19 +574,19 @@ moe_route_scores_kernel(const float* __restrict__ logits, const TB* __restrict__
 }
 
 KB_EXPORT int kb_moe_route_scores(const float* logits, const void* correction, int correction_is_bf16, int n, int K, int groups,
-                                  int keep, float scale, int* ids, float* weights, int T, cudaStream_t stream) {
+                                  int keep, float scale, int sigmoid, int stride, int* ids, float* weights, int T, cudaStream_t stream) {
     if (T == 0) return 0;
     if (!logits || !ids || !weights) return KB_ERR_NULL;
     if (n < 1 || K < 1 || K > n || n > MOE_MAX_EXPERTS) return KB_ERR_UNSUPPORTED_SIZE;
-    if (groups < 1 || n % groups != 0 || keep < 1 || keep > groups || K > keep * (n / groups)) return KB_ERR_BAD_ARG;
+    if (groups < 1 || n % groups != 0 || keep < 1 || keep > groups || K > keep * (n / groups) || stride < n) return KB_ERR_BAD_ARG;
     const size_t smem = (size_t)4 * (2 * n + groups) * sizeof(float);
     if (smem > 48 * 1024) return KB_ERR_UNSUPPORTED_SIZE;
     if (correction_is_bf16)
         kb_launch(moe_route_scores_kernel<__nv_bfloat16>, dim3((T + 3) / 4), dim3(128), smem, stream, logits, (const __nv_bfloat16*)correction,
-                  n, K, groups, keep, scale, ids, weights, T);
+                  n, K, groups, keep, scale, sigmoid, stride, ids, weights, T);
     else
         kb_launch(moe_route_scores_kernel<float>, dim3((T + 3) / 4), dim3(128), smem, stream, logits, (const float*)correction, n, K, groups,
-                  keep, scale, ids, weights, T);
+                  keep, scale, sigmoid, stride, ids, weights, T);
     return kb_launch_result();
 }
 
@@ -639,12 +672,13 @@ KB_EXPORT int kb_moe_skinny(const void* A, int lda, const int* sorted, int top, 
 }
 
 KB_EXPORT int kb_moe_combine(const void* rows, int rows_is_bf16, const float* weights, const int* at, int K, int H, void* out,
-                             int out_is_bf16, int T, const int* ids, const void* x, int real_experts, cudaStream_t stream) {
+                             int out_is_bf16, int T, const int* ids, const void* x, int real_experts, const void* extra,
+                             const float* extra_gate, int gate_stride, cudaStream_t stream) {
     if (T == 0) return 0;
-    if (!rows || !weights || !out || (ids && !x)) return KB_ERR_NULL;
+    if (!rows || !out || (ids && !x)) return KB_ERR_NULL;
 #define LAUNCH(TR, TO)                                                                                                     \
     kb_launch(moe_combine_kernel<TR, TO>, dim3(T), dim3(256), 0, stream, (const TR*)rows, weights, at, K, H, (TO*)out, ids, \
-              (const TO*)x, real_experts)
+              (const TO*)x, real_experts, (const TO*)extra, extra_gate, gate_stride)
     if (rows_is_bf16) {
         if (out_is_bf16) LAUNCH(__nv_bfloat16, __nv_bfloat16); else LAUNCH(__nv_bfloat16, float);
     } else {

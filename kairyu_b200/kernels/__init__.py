@@ -188,6 +188,36 @@ def rmsnorm(
     )
 
 
+def layernorm(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    bias: torch.Tensor,
+    eps: float,
+    out: torch.Tensor,
+    *,
+    delta: Optional[torch.Tensor] = None,
+    delta2: Optional[torch.Tensor] = None,
+    rows: Optional[torch.Tensor] = None,
+) -> None:
+    """``x += delta + delta2`` (those given; not with ``rows``), ``out = (x - mean) * rsqrt(var + eps) * weight + bias`` with the
+    variance the mean of the squared deviations, all in 32-bit.  ``x`` is the fp32 residual.  With ``rows`` only the listed rows
+    of x (+ the sums) are normed, into out[0..len(rows)), and x is not modified."""
+    _need_cuda("layernorm", x, weight, bias, out, delta, delta2, rows)
+    _need_i32("layernorm", rows)
+    H = x.shape[-1]
+    R = rows.numel() if rows is not None else x.shape[0]
+    if x.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous():
+        raise KernelError("layernorm: the residual must be contiguous fp32 and the output contiguous")
+    if weight.numel() != H or bias.numel() != H or weight.dtype != bias.dtype or out.shape[-1] != H or out.shape[0] < R:
+        raise KernelError("layernorm: shape mismatch, or weight and bias of different dtypes")
+    for pending in (delta, delta2):
+        if pending is not None and (pending.dtype != out.dtype or pending.shape != x.shape or not pending.is_contiguous()):
+            raise KernelError("layernorm: a pending sum must be contiguous, in the activation dtype and of x's shape")
+    fn = _fn("layernorm", "kb_layernorm", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p])
+    _check(fn(x.data_ptr(), _ptr(delta), _ptr(delta2), weight.data_ptr(), bias.data_ptr(), _is_bf16(weight, "layernorm"), out.data_ptr(),
+              _is_bf16(out, "layernorm"), _ptr(rows), R, H, float(eps), _stream()), "layernorm")
+
+
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     """out = silu(gate_up[:, :I]) * gate_up[:, I:]."""
     _need_cuda("swiglu", gate_up, out)
@@ -283,6 +313,71 @@ def qk_norm_rope_kv_write(
     )
 
 
+def projection_norm_rope_write(
+    packed: torch.Tensor,
+    *,
+    num_q_heads: int,
+    num_kv_heads: int,
+    head_dim: int,
+    value_dim: int,
+    k_offset: int,
+    v_offset: int,
+    positions: torch.Tensor,
+    row_ids: torch.Tensor,
+    q_norm_weight: Optional[torch.Tensor] = None,
+    k_norm_weight: Optional[torch.Tensor] = None,
+    eps: float = 0.0,
+    cos: Optional[torch.Tensor] = None,
+    sin: Optional[torch.Tensor] = None,
+    interleaved: bool = False,
+    block_table: Optional[torch.Tensor] = None,
+    write_from: Optional[torch.Tensor] = None,
+    k_cache: Optional[torch.Tensor] = None,
+    v_cache: Optional[torch.Tensor] = None,
+    flag: Optional[torch.Tensor] = None,
+) -> None:
+    """On the packed rows ``[q | ... k at k_offset ... v at v_offset ...]``: RMS norm of q over all its ``heads * dim``
+    columns at once and of k over all of its (if weights of those sizes are given), rotation of the first
+    ``2 * cos.shape[1]`` columns of every head (pairs (i, i + half), or (2i, 2i + 1) when ``interleaved``), q back in place, k
+    into ``k_cache`` [pages, page, kv_heads, dim] and v into ``v_cache`` [pages, page, kv_heads, value_dim]."""
+    what = "projection_norm_rope_write"
+    _need_cuda(what, packed, positions, row_ids, q_norm_weight, k_norm_weight, cos, sin, block_table, write_from, k_cache, v_cache, flag)
+    _need_i32(what, positions, row_ids, block_table, write_from)
+    q_size, k_size, v_size = num_q_heads * head_dim, num_kv_heads * head_dim, num_kv_heads * value_dim
+    if packed.stride(1) != 1 or k_offset < q_size or k_offset + k_size > packed.shape[1] or v_offset < 0 or v_offset + v_size > packed.shape[1]:
+        raise KernelError(f"{what}: the packed rows do not hold q, k and v where the offsets say")
+    rot_half = max_pos = 0
+    if cos is not None:
+        if sin is None or cos.shape != sin.shape or cos.dtype != torch.float32 or sin.dtype != torch.float32 or not (cos.is_contiguous() and sin.is_contiguous()):
+            raise KernelError(f"{what}: cos and sin must be contiguous fp32 tables of one shape")
+        max_pos, rot_half = cos.shape
+        if 2 * rot_half > head_dim:
+            raise KernelError(f"{what}: {2 * rot_half} rotated columns in a head of {head_dim}")
+    w_bf16 = 0
+    if q_norm_weight is not None:
+        if k_norm_weight is None or q_norm_weight.dtype != k_norm_weight.dtype or q_norm_weight.numel() != q_size or k_norm_weight.numel() != k_size \
+                or not (q_norm_weight.is_contiguous() and k_norm_weight.is_contiguous()):
+            raise KernelError(f"{what}: q and k norm weights come together, in one dtype, one entry a projection column")
+        w_bf16 = _is_bf16(q_norm_weight, what)
+    page_size = num_pages = max_pages = num_rows = 0
+    if k_cache is not None:
+        if v_cache is None or k_cache.dtype != packed.dtype or v_cache.dtype != packed.dtype or not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+            raise KernelError(f"{what}: contiguous caches in the activations' dtype")
+        num_pages, page_size = k_cache.shape[:2]
+        if tuple(k_cache.shape[2:]) != (num_kv_heads, head_dim) or tuple(v_cache.shape) != (num_pages, page_size, num_kv_heads, value_dim):
+            raise KernelError(f"{what}: cache geometry does not match the heads")
+        if block_table is None:
+            raise KernelError(f"{what}: a cache write needs the block table")
+        num_rows, max_pages = block_table.shape
+    fn = _fn("projection_rope", "kb_projection_norm_rope_write",
+             [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int,
+              c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(packed.data_ptr(), packed.stride(0), _is_bf16(packed, what), packed.shape[0], int(k_offset), int(v_offset), num_q_heads, num_kv_heads,
+              head_dim, value_dim, _ptr(q_norm_weight), _ptr(k_norm_weight), w_bf16, float(eps), _ptr(cos), _ptr(sin), rot_half, max_pos,
+              1 if interleaved else 0, positions.data_ptr(), row_ids.data_ptr(), _ptr(block_table), max_pages, _ptr(write_from), _ptr(k_cache),
+              _ptr(v_cache), page_size, num_pages, num_rows, _ptr(flag), _stream()), what)
+
+
 # ----------------------------------------------------------------------------- attention
 
 
@@ -299,13 +394,22 @@ def paged_attention_generic(
     scale: float,
     window: int = 0,
     flag: Optional[torch.Tensor] = None,
+    sinks: Optional[torch.Tensor] = None,
+    value_dim: Optional[int] = None,
+    out_head_stride: Optional[int] = None,
 ) -> None:
     """fp32-arithmetic attention of every token in ``q`` over its request's pages.
 
     ``q``: [tokens, >= heads*dim] (a view into the packed qkv rows is fine);
-    ``out``: [tokens, heads*dim].
+    ``out``: [tokens, heads*out_head_stride].  ``sinks``: fp32 [heads], a logit a head that joins the
+    softmax's denominator (a term exp(sink) there and nothing else).  ``value_dim`` (default: dim): how many
+    leading columns of a value row are used; with ``v_cache`` the key cache itself, a row's first
+    ``value_dim`` columns are its value.  ``out_head_stride`` (default: value_dim): where head h's
+    output starts in its token's row, h * out_head_stride (the columns behind value_dim stay as they are).
     """
-    _need_cuda("paged_attention_generic", q, out, k_cache, v_cache, positions, row_ids, block_table, flag)
+    _need_cuda("paged_attention_generic", q, out, k_cache, v_cache, positions, row_ids, block_table, flag, sinks)
+    if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != num_q_heads or not sinks.is_contiguous()):
+        raise KernelError("paged_attention_generic: sinks must be contiguous fp32, one a query head")
     _need_i32("paged_attention_generic", positions, row_ids, block_table)
     num_pages, page_size, num_kv_heads, head_dim = k_cache.shape
     if q.dtype != k_cache.dtype or out.dtype != q.dtype or v_cache.shape != k_cache.shape:
@@ -320,14 +424,15 @@ def paged_attention_generic(
     fn = _fn(
         "attention_generic",
         "kb_paged_attention_generic",
-        [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+        [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p],
     )
+    value_dim = int(head_dim if value_dim is None else value_dim)
     _check(
         fn(
             q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
             _is_bf16(q, "paged_attention_generic"), positions.data_ptr(), row_ids.data_ptr(), block_table.data_ptr(),
             block_table.shape[1], T, num_q_heads, num_kv_heads, head_dim, page_size, num_pages, float(scale),
-            int(window), _ptr(flag), _stream(),
+            int(window), _ptr(sinks), value_dim, int(value_dim if out_head_stride is None else out_head_stride), _ptr(flag), _stream(),
         ),
         "paged_attention_generic",
     )
@@ -381,6 +486,14 @@ def _check_diff_attention(what: str, q: torch.Tensor, out: torch.Tensor, k_cache
     return num_pages, page_size, num_kv_heads, dim, vdim
 
 
+def _check_sinks_gate(what: str, q: torch.Tensor, out: torch.Tensor, num_q_heads: int, sinks: Optional[torch.Tensor],
+                      gate: Optional[torch.Tensor]) -> None:
+    if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != num_q_heads or not sinks.is_contiguous()):
+        raise KernelError(f"{what}: sinks must be contiguous fp32, one a query head")
+    if gate is not None and (gate.dtype != q.dtype or gate.stride(1) != 1 or gate.shape[0] != q.shape[0] or gate.shape[1] < out.shape[1]):
+        raise KernelError(f"{what}: the gate must hold a column for every output column, in the activations' dtype")
+
+
 def diff_attention_generic(
     q: torch.Tensor,
     out: torch.Tensor,
@@ -399,35 +512,45 @@ def diff_attention_generic(
     head_norm_eps: Optional[float] = None,
     out_scale: float = 1.0,
     flag: Optional[torch.Tensor] = None,
+    sinks: Optional[torch.Tensor] = None,
+    gate: Optional[torch.Tensor] = None,
 ) -> None:
     """Attention with ``maps`` softmax maps a head over the same values, every token of the step, in 32-bit
     arithmetic.  ``q``: [tokens, >= heads * maps * dim], a head's maps side by side; the key cache
     [pages, page, kv_heads, maps * dim] the same way; values [pages, page, kv_heads, vdim].  Scores
     q.k * scale, capped as softcap * tanh(s / softcap) when softcap > 0; a token sees itself and the
     ``window - 1`` before it (0: all).  o = a_1 - lam * a_2; with ``head_norm_eps`` each head's o is divided
-    by its root mean square (eps inside the root) and multiplied by ``out_scale``.  ``out``: [tokens, heads * vdim]."""
+    by its root mean square (eps inside the root) and multiplied by ``out_scale``.  ``out``: [tokens, heads * vdim].
+    ``sinks``: fp32 [heads], a logit a head that joins every map's denominator (a term exp(sink) there and nothing else).
+    ``gate``: [tokens, >= heads * vdim] in the activations' dtype (a view into the packed rows is fine): the output
+    is multiplied by sigmoid(gate), last of all."""
     what = "diff_attention_generic"
-    _need_cuda(what, q, out, k_cache, v_cache, positions, row_ids, block_table, flag)
+    _need_cuda(what, q, out, k_cache, v_cache, positions, row_ids, block_table, flag, sinks, gate)
+    _check_sinks_gate(what, q, out, num_q_heads, sinks, gate)
     _need_i32(what, positions, row_ids, block_table)
     num_pages, page_size, num_kv_heads, dim, vdim = _check_diff_attention(what, q, out, k_cache, v_cache, num_q_heads, maps)
     if dim > 256 or vdim > 256:
         raise KernelError(f"{what}: key width {dim} or value width {vdim} > 256 is not supported")
     fn = _fn("diff_attention", "kb_diff_attention_generic",
              [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-              c_int, c_int, c_int, c_float, c_float, c_int, c_float, c_int, c_float, c_float, c_void_p, c_void_p])
+              c_int, c_int, c_int, c_float, c_float, c_int, c_float, c_int, c_float, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p])
     _check(fn(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), _is_bf16(q, what),
               positions.data_ptr(), row_ids.data_ptr(), block_table.data_ptr(), block_table.shape[1], q.shape[0], num_q_heads, num_kv_heads,
               int(maps), dim, vdim, page_size, num_pages, float(scale), float(softcap), int(window), float(lam),
-              0 if head_norm_eps is None else 1, float(head_norm_eps or 0.0), float(out_scale), _ptr(flag), _stream()), what)
+              0 if head_norm_eps is None else 1, float(head_norm_eps or 0.0), float(out_scale), _ptr(sinks), _ptr(gate),
+              gate.stride(0) if gate is not None else 0, _ptr(flag), _stream()), what)
 
 
 DIFF_ATTENTION_TILE = 64  # queries a tile of the tensor-core kernel for prompt portions
 
 
-def diff_attention_mma_supported(head_dim: int, value_dim: int, num_q_heads: int, num_kv_heads: int) -> bool:
+DIFF_ATTENTION_MMA_MAPS = (2,)  # how many softmax maps a head the tensor-core kernel is built for
+
+
+def diff_attention_mma_supported(head_dim: int, value_dim: int, num_q_heads: int, num_kv_heads: int, maps: int = 2) -> bool:
     """Sizes the tensor-core kernel of differential attention takes (bfloat16; key and value widths multiples of 16
     up to 128, up to 64 query heads a key/value head); others use the 32-bit-arithmetic kernel."""
-    return (head_dim % 16 == 0 and 16 <= head_dim <= 128 and value_dim % 16 == 0 and 16 <= value_dim <= 128
+    return (maps in DIFF_ATTENTION_MMA_MAPS and head_dim % 16 == 0 and 16 <= head_dim <= 128 and value_dim % 16 == 0 and 16 <= value_dim <= 128
             and num_kv_heads >= 1 and num_q_heads % num_kv_heads == 0 and num_q_heads // num_kv_heads <= 64)
 
 
@@ -474,6 +597,8 @@ def diff_attention_mma(
     if ctx.num_decode_rows:
         launch(ctx.decode_rows, ctx.decode_tokens, ctx.num_decode_rows, 1)
 
+
+ATTENTION_MMA_SINKS = False  # whether the tensor-core attention kernels take sink logits; until they do, the 32-bit-arithmetic kernel runs
 
 DECODE_SPLIT = 128  # keys per split of the split-KV kernel (csrc/attention_mma.cu: DEC_SPLIT)
 
@@ -1291,6 +1416,19 @@ __all__ = [
 
 
 @dataclass
+class PendingSums:
+    """What a layer whose sub-layers run side by side leaves for the next norm: two outputs still to be added to the
+    residual (the mixer's, then the feed-forward's).  A norm that takes two pending sums adds both in its own kernel."""
+
+    first: torch.Tensor
+    second: torch.Tensor
+
+    @property
+    def shape(self) -> torch.Size:
+        return self.first.shape
+
+
+@dataclass
 class ResidualCopy:
     """What a block that norms its sub-layers' OUTPUTS hands to the block after it: the residual's
     rows in the activation dtype (the sub-layers read the stream itself, so the next one wants them
@@ -1359,38 +1497,72 @@ def latent_norm_write(
     rank: int,
     weight: torch.Tensor,
     eps: float,
-    cache: torch.Tensor,
+    cache: Optional[torch.Tensor],
     *,
     positions: torch.Tensor,
     row_ids: torch.Tensor,
-    block_table: torch.Tensor,
+    block_table: Optional[torch.Tensor],
     write_from: Optional[torch.Tensor],
     flag: Optional[torch.Tensor] = None,
+    rot_dim: int = 0,
+    cos: Optional[torch.Tensor] = None,
+    sin: Optional[torch.Tensor] = None,
+    interleaved: bool = True,
+    q_out: Optional[torch.Tensor] = None,
+    num_heads: int = 0,
+    q_head_width: int = 0,
 ) -> None:
     """Columns [offset, offset + rank) of every row of ``packed`` are RMS-normed (32-bit) and written,
-    in the cache's dtype, at the token's place in its request's pages.  ``cache``: [pages, page_size, 1, rank]."""
-    _need_cuda("latent_norm_write", packed, weight, cache, positions, row_ids, block_table, write_from, flag)
+    in the cache's dtype, at the token's place in its request's pages.  ``cache``: [pages, page_size, 1, rank + rot_dim].
+
+    ``rot_dim`` > 0: the ``rot_dim`` columns behind the latent's are one key part shared by all heads; it is
+    rotated by the token's position (``cos``/``sin`` [positions, rot_dim/2] fp32; pairs (2i, 2i+1) when
+    ``interleaved``, else (i, i + rot_dim/2)) and stored behind the latent.  With ``q_out``
+    [tokens, heads * (rank + rot_dim)] the last ``rot_dim`` of every head's ``q_head_width`` columns of the
+    packed query (columns [0, heads * q_head_width)) are rotated into columns [rank, rank + rot_dim) of the
+    head's row of ``q_out``.  ``cache=None``: only the queries' part is produced (a call that writes no cache)."""
+    _need_cuda("latent_norm_write", packed, weight, cache, positions, row_ids, block_table, write_from, flag, cos, sin, q_out)
     _need_i32("latent_norm_write", positions, row_ids, block_table, write_from)
-    num_pages, page_size, heads, width = cache.shape
-    if heads != 1 or width != rank or not cache.is_contiguous() or cache.dtype != packed.dtype:
-        raise KernelError("latent_norm_write: the cache must be contiguous [pages, page_size, 1, rank] in the activations' dtype")
-    if packed.stride(1) != 1 or offset < 0 or offset + rank > packed.shape[1] or weight.numel() != rank:
+    width = rank + rot_dim
+    num_pages = page_size = 1
+    if cache is not None:
+        num_pages, page_size, heads, cache_width = cache.shape
+        if heads != 1 or cache_width != width or not cache.is_contiguous() or cache.dtype != packed.dtype:
+            raise KernelError("latent_norm_write: the cache must be contiguous [pages, page_size, 1, rank + rot_dim] in the activations' dtype")
+        if block_table is None:
+            raise KernelError("latent_norm_write: a cache write needs the block table")
+    if packed.stride(1) != 1 or offset < 0 or offset + width > packed.shape[1] or weight.numel() != rank:
         raise KernelError("latent_norm_write: the packed rows do not hold the latent's columns")
+    max_pos = 0
+    if rot_dim:
+        if cos is None or sin is None or cos.shape != sin.shape or cos.shape[1] * 2 != rot_dim or cos.dtype != torch.float32 or sin.dtype != torch.float32 \
+                or not (cos.is_contiguous() and sin.is_contiguous()):
+            raise KernelError("latent_norm_write: cos and sin must be contiguous fp32 [positions, rot_dim / 2]")
+        max_pos = cos.shape[0]
+        if q_out is not None:
+            if q_out.dtype != packed.dtype or q_out.stride(1) != 1 or q_out.shape[1] != num_heads * width or q_out.shape[0] != packed.shape[0] \
+                    or q_head_width < rot_dim or num_heads * q_head_width > packed.shape[1]:
+                raise KernelError("latent_norm_write: q_out must be [tokens, heads * (rank + rot_dim)] beside a packed query of heads * q_head_width columns")
+    elif q_out is not None:
+        raise KernelError("latent_norm_write: q_out comes with a rotated part")
     fn = _fn("latent_cache", "kb_latent_norm_write",
              [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-              c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+              c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p])
     _check(
         fn(packed.data_ptr(), packed.stride(0), int(offset), int(rank), _is_bf16(packed, "latent_norm_write"), weight.data_ptr(),
-           _is_bf16(weight, "latent_norm_write"), float(eps), positions.data_ptr(), row_ids.data_ptr(), block_table.data_ptr(),
-           block_table.shape[1], _ptr(write_from), cache.data_ptr(), page_size, num_pages, block_table.shape[0], packed.shape[0],
-           _ptr(flag), _stream()),
+           _is_bf16(weight, "latent_norm_write"), float(eps), positions.data_ptr(), row_ids.data_ptr(), _ptr(block_table),
+           block_table.shape[1] if block_table is not None else 0, _ptr(write_from), _ptr(cache), page_size, num_pages,
+           block_table.shape[0] if block_table is not None else 0, packed.shape[0], int(rot_dim), _ptr(cos), _ptr(sin), max_pos,
+           1 if interleaved else 0, int(num_heads), int(q_head_width), _ptr(q_out), q_out.stride(0) if q_out is not None else 0,
+           1 if cache is not None else 0, _ptr(flag), _stream()),
         "latent_norm_write",
     )
 
 
 def heads_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
     """A product per head: ``out[t, h, :] = weight[h] @ x[t, h, :]``.  ``x`` [tokens, heads, K] and
-    ``out`` [tokens, heads, N] may be views with any row stride (inner stride 1); ``weight`` is
+    ``out`` [tokens, heads, N] may be views with any row and head stride (inner stride 1: a head's columns
+    may be part of a wider run); ``weight`` is
     contiguous [heads, N, K].  bfloat16: the library's batched product (fp32 accumulation);
     float32: this package's FMA product, one launch a head."""
     _need_cuda("heads_linear", x, weight, out)
@@ -1398,8 +1570,8 @@ def heads_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> No
     N = weight.shape[1]
     if weight.shape != (H, N, K) or out.shape != (T, H, N) or not weight.is_contiguous():
         raise KernelError(f"heads_linear: shapes x{tuple(x.shape)} w{tuple(weight.shape)} out{tuple(out.shape)} do not agree")
-    if x.stride(2) != 1 or out.stride(2) != 1 or x.stride(1) != K or out.stride(1) != N:
-        raise KernelError("heads_linear: a token's heads must lie side by side")
+    if x.stride(2) != 1 or out.stride(2) != 1 or x.stride(1) < K or out.stride(1) < N:
+        raise KernelError("heads_linear: a head's columns must lie side by side, and heads must not overlap")
     if T == 0:
         return
     if x.dtype == torch.float32:
@@ -1407,7 +1579,7 @@ def heads_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> No
             raise KernelError("heads_linear: the 32-bit path needs fp32 weights and output")
         fn = _fn("gemm_f32", "kb_gemm_f32", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
         for h in range(H):
-            _check(fn(x.data_ptr() + 4 * h * K, x.stride(0), weight.data_ptr() + 4 * h * N * K, K, None, out.data_ptr() + 4 * h * N,
+            _check(fn(x.data_ptr() + 4 * h * x.stride(1), x.stride(0), weight.data_ptr() + 4 * h * N * K, K, None, out.data_ptr() + 4 * h * out.stride(1),
                       out.stride(0), T, N, K, _stream()), "heads_linear")
         return
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
@@ -1532,21 +1704,42 @@ def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int, ids:
 
 
 def moe_route_scores(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int, ids: torch.Tensor, weights: torch.Tensor, *,
-                     groups: int = 1, keep: int = 1, scale: float = 1.0) -> None:
-    """Routing by scores (fp32): s = softmax(logits) over all outputs; the choice runs on s + correction within the
-    ``keep`` best of ``groups`` equal groups of neighbours (a group's value: its largest s + correction); the ``top``
-    best are chosen (ties: the lower index) and weigh s * scale, not renormalised."""
+                     groups: int = 1, keep: int = 1, scale: float = 1.0, score: str = "softmax") -> None:
+    """Routing by scores (fp32): s = softmax(logits) over all outputs (``score="sigmoid"``: s = sigmoid(logit), each output by
+    itself); the choice runs on s + correction within the ``keep`` best of ``groups`` equal groups of neighbours (a group's
+    value: its largest s + correction); the ``top`` best are chosen (ties: the lower index) and weigh s * scale, not
+    renormalised.  ``logits`` may be the leading columns of wider rows (a view ``[:, :n]``)."""
     _need_cuda("moe_route_scores", logits, correction, ids, weights)
     T, n = logits.shape
-    if logits.dtype != torch.float32 or not logits.is_contiguous() or weights.dtype != torch.float32 or ids.dtype != torch.int32:
+    if score not in ("softmax", "sigmoid"):
+        raise KernelError(f"moe_route_scores: unknown score function {score!r} (softmax, sigmoid)")
+    if logits.dtype != torch.float32 or logits.stride(1) != 1 or weights.dtype != torch.float32 or ids.dtype != torch.int32:
         raise KernelError("moe_route_scores: fp32 logits and weights, int32 ids")
     if ids.shape != (T, top) or weights.shape != (T, top) or not ids.is_contiguous() or not weights.is_contiguous():
         raise KernelError("moe_route_scores: ids and weights must be contiguous [tokens, top]")
     if correction is not None and (correction.numel() != n or not correction.is_contiguous()):
         raise KernelError("moe_route_scores: the correction must have one entry a router output")
-    fn = _fn("moe", "kb_moe_route_scores", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p])
+    fn = _fn("moe", "kb_moe_route_scores", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
     _check(fn(logits.data_ptr(), _ptr(correction), _is_bf16(correction, "moe_route_scores") if correction is not None else 0, n, int(top),
-              int(groups), int(keep), float(scale), ids.data_ptr(), weights.data_ptr(), T, _stream()), "moe_route_scores")
+              int(groups), int(keep), float(scale), 1 if score == "sigmoid" else 0, logits.stride(0) if T > 1 else n, ids.data_ptr(),
+              weights.data_ptr(), T, _stream()), "moe_route_scores")
+
+
+def moe_scale_rows(src: torch.Tensor, scale: torch.Tensor, out: torch.Tensor, *, rows: Optional[torch.Tensor] = None, per: int = 1,
+                   index: Optional[torch.Tensor] = None) -> None:
+    """out[i] = src[rows[i]] * scale[index[i]] (``rows=None``: src[i // per]; ``index=None``: scale[i]), 32-bit with one
+    rounding: the input rows of experts whose router weight multiplies their input.  ``scale``: flat fp32."""
+    _need_cuda("moe_scale_rows", src, scale, out, rows, index)
+    _need_i32("moe_scale_rows", rows, index)
+    R, H = out.shape
+    if src.dtype != out.dtype or src.shape[1] != H or not (src.is_contiguous() and out.is_contiguous()):
+        raise KernelError("moe_scale_rows: contiguous rows of one width and dtype")
+    if scale.dtype != torch.float32 or not scale.is_contiguous() or (index is None and scale.numel() < R) or (rows is not None and rows.numel() < R) \
+            or (index is not None and index.numel() < R) or (rows is None and (R + per - 1) // per > src.shape[0]):
+        raise KernelError("moe_scale_rows: a weight and a source row for every output row")
+    fn = _fn("moe", "kb_moe_scale_rows", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(src.data_ptr(), _is_bf16(src, "moe_scale_rows"), _ptr(rows), int(per), scale.data_ptr(), _ptr(index), out.data_ptr(), R, H,
+              _stream()), "moe_scale_rows")
 
 
 def moe_plan(ids: torch.Tensor, experts: int, plan: torch.Tensor) -> dict:
@@ -1660,19 +1853,35 @@ def moe_skinny(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, plan: d
               plan["max_tiles"], float(limit), float(alpha), float(shift), experts, out.data_ptr(), _stream()), "moe_skinny")
 
 
-def moe_combine(rows: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, at: Optional[torch.Tensor] = None, *,
-                ids: Optional[torch.Tensor] = None, x: Optional[torch.Tensor] = None, experts: int = 0) -> None:
+def moe_combine(rows: torch.Tensor, weights: Optional[torch.Tensor], out: torch.Tensor, at: Optional[torch.Tensor] = None, *,
+                ids: Optional[torch.Tensor] = None, x: Optional[torch.Tensor] = None, experts: int = 0, top: Optional[int] = None,
+                extra: Optional[torch.Tensor] = None, extra_gate: Optional[torch.Tensor] = None) -> None:
     """out[t] = sum_k weights[t, k] * rows[t * K + k] (or rows[at[t * K + k]]): fp32 sum, in the order of k.  With ``ids``
     [tokens, K], ``x`` [tokens, H] (out's dtype) and ``experts``: a pair whose id is ``experts`` or more is an identity
-    expert and contributes the token's own row ``x[t]``."""
-    _need_cuda("moe_combine", rows, weights, out, at, ids, x)
+    expert and contributes the token's own row ``x[t]``.  ``weights=None`` (then ``top`` names K): a plain sum.  ``extra``
+    [tokens, H] (out's dtype): an always-on expert's rows, added last, times sigmoid(``extra_gate[t]``) when that
+    (fp32, one number a token, any row stride) is given."""
+    _need_cuda("moe_combine", rows, weights, out, at, ids, x, extra, extra_gate)
     _need_i32("moe_combine", at, ids)
-    if ids is not None and (x is None or x.dtype != out.dtype or x.shape != out.shape or not x.is_contiguous() or ids.shape != weights.shape):
+    T, H = out.shape
+    if weights is None:
+        if top is None:
+            raise KernelError("moe_combine: a plain sum needs the number of rows a token")
+        K = int(top)
+    else:
+        K = weights.shape[1]
+        if weights.dtype != torch.float32 or weights.shape[0] != T or not weights.is_contiguous():
+            raise KernelError("moe_combine: weights must be contiguous fp32 [tokens, K]")
+    if ids is not None and (x is None or x.dtype != out.dtype or x.shape != out.shape or not x.is_contiguous() or ids.shape != (T, K)):
         raise KernelError("moe_combine: identity experts need the tokens' rows in the output's dtype and shape, and ids [tokens, K]")
-    T, K = weights.shape
-    H = rows.shape[1]
-    if weights.dtype != torch.float32 or rows.shape[0] != T * K or out.shape != (T, H) or not (rows.is_contiguous() and weights.is_contiguous() and out.is_contiguous()):
+    if rows.shape != (T * K, H) or not (rows.is_contiguous() and out.is_contiguous()):
         raise KernelError("moe_combine: shape or dtype mismatch")
-    fn = _fn("moe", "kb_moe_combine", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
-    _check(fn(rows.data_ptr(), _is_bf16(rows, "moe_combine"), weights.data_ptr(), _ptr(at), K, H, out.data_ptr(), _is_bf16(out, "moe_combine"), T,
-              _ptr(ids), _ptr(x), int(experts), _stream()), "moe_combine")
+    if extra is not None and (extra.dtype != out.dtype or extra.shape != out.shape or not extra.is_contiguous()):
+        raise KernelError("moe_combine: the extra rows must have the output's dtype and shape")
+    if extra_gate is not None and (extra is None or extra_gate.dtype != torch.float32 or extra_gate.shape[0] != T):
+        raise KernelError("moe_combine: the extra rows' gate is fp32, one number a token")
+    fn = _fn("moe", "kb_moe_combine", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
+                                        c_void_p, c_void_p, c_int, c_void_p])
+    _check(fn(rows.data_ptr(), _is_bf16(rows, "moe_combine"), _ptr(weights), _ptr(at), K, H, out.data_ptr(), _is_bf16(out, "moe_combine"), T,
+              _ptr(ids), _ptr(x), int(experts), _ptr(extra), _ptr(extra_gate), extra_gate.stride(0) if extra_gate is not None else 0,
+              _stream()), "moe_combine")

@@ -43,6 +43,8 @@ LIBRARIES: dict[str, list[str]] = {
     "sampling": [],
     "sublayer_norm": [],
     "latent_cache": [],
+    "layernorm": [],
+    "projection_rope": [],
     "delta_rule": [],
     "moe": [],
 }

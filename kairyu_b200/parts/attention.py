@@ -61,8 +61,14 @@ def run_paged_attention(
     head_dim: int,
     scale: float,
     window: int,
+    sinks: Optional[torch.Tensor] = None,
+    value_dim: Optional[int] = None,
 ) -> None:
     """Attention of every token of the step; picks the kernels for the dtype.
+
+    ``sinks`` (fp32, one logit a query head) joins every softmax's denominator.  ``value_dim``: a value
+    is the first ``value_dim`` columns of its row (for a cache whose rows serve as keys and values);
+    ``out`` keeps ``head_dim`` columns a head either way, of which the first ``value_dim`` are the result.
 
     float32: the fp32 kernel for all tokens (its arithmetic per token does not
     depend on the batch).  bfloat16: tensor-core kernels, query tiles for
@@ -74,6 +80,7 @@ def run_paged_attention(
         qkv.dtype == torch.bfloat16
         and kernels.attention_mma_supported(head_dim, num_q_heads, num_kv_heads)
         and not ctx.extras.get("force_generic_attention", False)
+        and (sinks is None or kernels.ATTENTION_MMA_SINKS)
     )
     if not use_mma:
         kernels.paged_attention_generic(
@@ -88,6 +95,9 @@ def run_paged_attention(
             scale=scale,
             window=window,
             flag=ctx.error_flag,
+            sinks=sinks,
+            value_dim=value_dim,
+            out_head_stride=head_dim,
         )
         return
     num_tiles, tile_rows, tile_starts = ctx.tiles[kernels.attention_prefill_tile_rows(head_dim)]

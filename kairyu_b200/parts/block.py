@@ -148,3 +148,41 @@ class OutputNormBlock(Block):
                 output = self.ffn.forward(rows, ctx)
             rows = self.ffn_norm.add_normed(residual, output, ctx)
         return residual, (None if rows is residual else kernels.ResidualCopy(rows))
+
+
+@BLOCKS.register("parallel")
+class ParallelBlock(Block):
+    """``h = norm(x); x += mixer(h) + ffn(h)``: one norm a layer, and both sub-layers read its output.  A layer may have no
+    feed-forward.
+
+    The residual is fp32.  The two outputs are handed on unsummed (``kernels.PendingSums``) and the next norm's kernel adds
+    them to the residual, in 32-bit, on its way, so the layer's sum costs no kernel of its own; the norm must be one that
+    takes two pending sums (``layernorm`` does)."""
+
+    graph_safe = True
+
+    def __init__(self, *, layer: LayerSpec, dtype: torch.dtype, device: str, shared: dict, **_: object) -> None:
+        context = dict(dtype=dtype, device=device, shared=shared)
+        self.mixer_norm = NORMS.build(layer.mixer_norm, **context)
+        self.mixer = MIXERS.build(layer.mixer, **context)
+        self.ffn = FEED_FORWARDS.build(layer.ffn, **context) if layer.ffn is not None else None
+        if layer.ffn_norm is not None:
+            raise ValueError("a parallel layer has one norm; its feed-forward reads the mixer's input")
+        self._parts = tuple(part for part in (self.mixer_norm, self.mixer, self.ffn) if part is not None)
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return [spec for part in self._parts for spec in part.tensor_specs()]
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        for part in self._parts:
+            part.load(tensors)
+
+    def bytes_streamed(self) -> int:
+        return sum(part.bytes_streamed() for part in self._parts)
+
+    def forward(self, residual: torch.Tensor, delta, ctx: StepContext, cache: CacheView):
+        normed = self.mixer_norm.apply(residual, delta, ctx)
+        mixed = self.mixer.forward(normed, ctx, cache)
+        if self.ffn is None:
+            return residual, mixed
+        return residual, kernels.PendingSums(mixed, self.ffn.forward(normed, ctx))

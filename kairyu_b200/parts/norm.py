@@ -1,4 +1,4 @@
-"""RMSNorm with the residual sum fused in (kairyu/models/layers.py:21-46)."""
+"""Norms with the residual sum fused in: RMSNorm (kairyu/models/layers.py:21-46) and layer norm with weight and bias."""
 
 from __future__ import annotations
 
@@ -71,3 +71,51 @@ class RMSNorm(Norm):
         values = ctx.workspace.buffer(f"norm.fold.{tag}.values", rows, self.size, torch.bfloat16)
         sumsq = ctx.workspace.flat(f"norm.fold.{tag}.sumsq", 16 * kernels.skinny_blocks(rows, self.size), torch.float32).view(-1, 16)
         return kernels.ResidualNorm(residual, self.weight, self.eps, values, sumsq)
+
+
+@NORMS.register("layernorm")
+class LayerNorm(Norm):
+    """``y = (x - mean(x)) * rsqrt(mean((x - mean(x))^2) + eps) * weight + bias`` with fp32 statistics.  The bias is the tensor
+    ``bias_name`` (default: the weight's name + ``.b``).  ``apply`` takes one pending sum or two (``kernels.PendingSums``:
+    a layer whose mixer and feed-forward ran side by side) and adds them in the same kernel."""
+
+    graph_safe = True
+
+    def __init__(self, *, name: str, size: int, eps: float, dtype: torch.dtype, device: str, bias_name: Optional[str] = None, **_: object) -> None:
+        self.name = name
+        self.bias_name = bias_name or f"{name}.b"
+        self.size = size
+        self.eps = float(eps)
+        self.dtype = dtype
+        self.device = device
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return [
+            TensorSpec(self.name, (self.size,), role="vector", init="norm"),
+            TensorSpec(self.bias_name, (self.size,), role="vector", init="normal"),
+        ]
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.weight = tensors[self.name].contiguous()
+        self.bias = tensors[self.bias_name].contiguous()
+        if self.weight.dtype != self.bias.dtype:  # one of them stored in 32-bit: both are held so
+            self.weight, self.bias = self.weight.float(), self.bias.float()
+
+    def bytes_streamed(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.weight, self.bias))
+
+    def apply(
+        self,
+        residual: torch.Tensor,
+        delta,
+        ctx: StepContext,
+        *,
+        rows: Optional[torch.Tensor] = None,
+    ) -> torch.Tensor:
+        count = rows.numel() if rows is not None else residual.shape[0]
+        out = ctx.workspace.buffer("norm.out" if rows is None else "norm.rows.out", count, self.size, self.dtype)
+        first, second = (delta.first, delta.second) if isinstance(delta, kernels.PendingSums) else (delta, None)
+        kernels.layernorm(residual, self.weight, self.bias, self.eps, out, delta=first, delta2=second, rows=rows)
+        return out

@@ -66,9 +66,17 @@ def _yarn_inv_freq(dim: int, theta: float, scaling: RopeScaling) -> tuple[torch.
 
 
 def rotary_tables(
-    dim: int, theta: float, scaling: Optional[RopeScaling], max_positions: int
+    dim: int, theta: float, scaling: Optional[RopeScaling], max_positions: int, wide_angles: bool = False
 ) -> tuple[torch.Tensor, torch.Tensor]:
-    """(cos, sin), each [max_positions, dim/2] fp32, on the CPU."""
+    """(cos, sin), each [max_positions, dim/2] fp32, on the CPU.  ``wide_angles``: frequencies theta^(-2i/dim) and
+    angles position * frequency are formed in 64-bit and only cos and sin are rounded to 32-bit, so that an entry
+    is the correctly rounded value at every position (no scaling kinds)."""
+    if wide_angles:
+        if scaling is not None:
+            raise ValueError("wide angles come without frequency scaling")
+        inv_freq = theta ** (-torch.arange(0, dim, 2, dtype=torch.float64) / dim)
+        freqs = torch.arange(max_positions, dtype=torch.float64)[:, None] * inv_freq[None, :]
+        return freqs.cos().float().contiguous(), freqs.sin().float().contiguous()
     factor = 1.0
     if scaling is not None and scaling.kind == "yarn":
         inv_freq, factor = _yarn_inv_freq(dim, theta, scaling)
@@ -93,13 +101,14 @@ class RotaryEncoding(PositionEncoding):
         scaling: Optional[RopeScaling],
         max_positions: int,
         device: str,
+        wide_angles: bool = False,
         **_: object,
     ) -> None:
         if rotary_dim % 2:
             raise ValueError(f"rotary_dim must be even, got {rotary_dim}")
         self.rotary_dim = rotary_dim
         self.max_positions = max_positions
-        cos, sin = rotary_tables(rotary_dim, theta, scaling, max_positions)
+        cos, sin = rotary_tables(rotary_dim, theta, scaling, max_positions, wide_angles)
         self.cos = cos.to(device)
         self.sin = sin.to(device)
 

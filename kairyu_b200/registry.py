@@ -65,6 +65,9 @@ def _register_builtin() -> None:
     from kairyu_b200.models import karesun
 
     register_architecture("Karesun", karesun.parse_karesun, karesun.karesun_spec)
+    from kairyu_b200.models import mapalorn
+
+    register_architecture("Mapalorn", mapalorn.parse_mapalorn, mapalorn.mapalorn_spec)
 
 
 _register_builtin()

@@ -66,11 +66,12 @@ def diff_attention_generic(q, out, k_cache, v_cache, *, positions, row_ids, bloc
             out[t, h * vdim : (h + 1) * vdim] = o.to(out.dtype)
 
 
-def moe_route_scores(logits, correction, top, ids, weights, *, groups=1, keep=1, scale=1.0):
+def moe_route_scores(logits, correction, top, ids, weights, *, groups=1, keep=1, scale=1.0, score="softmax"):
     outputs = logits.shape[1]
     per = outputs // groups
     for t in range(logits.shape[0]):
-        s = torch.softmax(logits[t].float(), dim=0)
+        z = logits[t].float()
+        s = torch.sigmoid(z) if score == "sigmoid" else torch.softmax(z, dim=0)
         c = s + (correction.float() if correction is not None else 0.0)
         values = [float(c[g * per : (g + 1) * per].max()) for g in range(groups)]
         kept = sorted(range(groups), key=lambda g: (-values[g], g))[:keep]
@@ -96,8 +97,9 @@ def moe_grouped(a, weight, out, plan, *, top, gated, limit=0.0, alpha=1.702, shi
             out[pair] = w @ a[place].float()
 
 
-def moe_combine(rows, weights, out, at=None, *, ids=None, x=None, experts=0):
-    tokens, top = weights.shape
+def moe_combine(rows, weights, out, at=None, *, ids=None, x=None, experts=0, top=None, extra=None, extra_gate=None):
+    tokens = out.shape[0]
+    top = weights.shape[1] if weights is not None else top
     picked = rows.float() if at is None else rows.float()[at.long()]
     picked = picked.view(tokens, top, -1).clone()
     if ids is not None:
@@ -105,7 +107,10 @@ def moe_combine(rows, weights, out, at=None, *, ids=None, x=None, experts=0):
             for k in range(top):
                 if int(ids[t, k]) >= experts:
                     picked[t, k] = x[t].float()
-    out.copy_((picked * weights.unsqueeze(-1)).sum(1).to(out.dtype))
+    total = (picked * weights.unsqueeze(-1)).sum(1) if weights is not None else picked.sum(1)
+    if extra is not None:
+        total = total + extra.float() * (torch.sigmoid(extra_gate.float().reshape(tokens, 1)) if extra_gate is not None else 1.0)
+    out.copy_(total.to(out.dtype))
 
 
 _NAMES = ["add_positions", "activation", "paged_kv_write", "diff_attention_generic", "moe_route_scores", "moe_grouped", "moe_combine"]

@@ -109,8 +109,11 @@ def _attend_token(q_t, k_cache, v_cache, table, pos, num_q_heads, scale, window)
     return torch.einsum("hk,khd->hd", probs, v)
 
 
-def paged_attention_generic(q, out, k_cache, v_cache, *, positions, row_ids, block_table, num_q_heads, scale, window=0, flag=None):
+def paged_attention_generic(q, out, k_cache, v_cache, *, positions, row_ids, block_table, num_q_heads, scale, window=0, flag=None,
+                            sinks=None, value_dim=None, out_head_stride=None):
     dim = k_cache.shape[-1]
+    # sinks and values narrower than their rows are stated in mapalorn_torch_kernels
+    assert sinks is None and value_dim in (None, dim) and out_head_stride in (None, dim)
     for t in range(q.shape[0]):
         q_t = q[t, : num_q_heads * dim].float().view(num_q_heads, dim)
         res = _attend_token(q_t, k_cache, v_cache, block_table[int(row_ids[t])], int(positions[t]), num_q_heads, scale, window)
