@@ -78,6 +78,6 @@ KB_EXPORT int kb_attention_decode_mma_static(const void* q, int q_stride, void* 
     dim3 grid(num_rows, Hq);
     kb_launch(attention_decode_merge_kernel, dim3(grid), dim3(128), 0, stream, part_o, part_ml, seq_lens, decode_rows, decode_tokens,
                                                             (__nv_bfloat16*)out, out_stride, Hq, D, window,
-                                                            (int)num_splits);
+                                                            (int)num_splits, (const float*)nullptr, (const __nv_bfloat16*)nullptr, 0);
     return kb_launch_result();
 }

@@ -6,8 +6,8 @@ KB_EXPORT int kb_attention_prefill_mma(const void* q, int q_stride, void* out, i
                                        const int* qo_indptr, const int* seq_lens,
                                        const int* block_table, int max_pages, const int* tile_rows,
                                        const int* tile_starts, int num_tiles, int Hq, int Hkv, int D,
-                                       int page_size, int num_pages, float scale, int window, int* flag,
-                                       cudaStream_t stream) {
+                                       int page_size, int num_pages, float scale, int window, const float* sinks,
+                                       const void* gate, int gate_stride, int* flag, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
     if (!q || !out || !k_cache || !v_cache || !qo_indptr || !seq_lens || !block_table || !tile_rows || !tile_starts) return KB_ERR_NULL;
     if (Hkv < 1 || Hq % Hkv != 0 || num_tiles > 65535) return KB_ERR_BAD_ARG;
@@ -15,7 +15,7 @@ KB_EXPORT int kb_attention_prefill_mma(const void* q, int q_stride, void* out, i
     const int dp = padded_dim(D);
 #define ARGS (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_cache, \
              (const __nv_bfloat16*)v_cache, qo_indptr, seq_lens, block_table, max_pages, tile_rows,       \
-             tile_starts, num_tiles, Hq, Hkv, D, page_size, num_pages, scale, window, flag, stream
+             tile_starts, num_tiles, Hq, Hkv, D, page_size, num_pages, scale, window, sinks, (const __nv_bfloat16*)gate, gate_stride, flag, stream
     switch (dp) {
         case 32: return launch_prefill<32, 2>(ARGS);
         case 64: return launch_prefill<64, 2>(ARGS);
@@ -27,13 +27,15 @@ KB_EXPORT int kb_attention_prefill_mma(const void* q, int q_stride, void* out, i
 }
 
 // part_o: [rows, Hq, splits, D] fp32; part_ml: [rows, Hq, splits, 2] fp32 (scratch).
+// sinks (both entry points; optional): one fp32 logit a query head whose exp joins the softmax's denominator.
+// gate (both; optional): bf16 [tokens, gate_stride], columns laid out as out's; the result is multiplied by its sigmoid.
 KB_EXPORT int kb_attention_decode_mma(const void* q, int q_stride, void* out, int out_stride,
                                       const void* k_cache, const void* v_cache, const int* seq_lens,
                                       const int* block_table, int max_pages, const int* decode_rows,
                                       const int* decode_tokens, int num_rows, int Hq, int Hkv, int D,
                                       int page_size, int num_pages, float scale, int window,
-                                      int num_splits, float* part_o, float* part_ml, int* flag,
-                                      cudaStream_t stream) {
+                                      int num_splits, float* part_o, float* part_ml, const float* sinks,
+                                      const void* gate, int gate_stride, int* flag, cudaStream_t stream) {
     if (num_rows == 0) return 0;
     if (!q || !out || !k_cache || !v_cache || !seq_lens || !block_table || !decode_rows || !decode_tokens || !part_o || !part_ml) return KB_ERR_NULL;
     if (Hkv < 1 || Hq % Hkv != 0 || Hq / Hkv > 16 || Hkv > 65535 || num_splits < 1 || num_splits > 65535) return KB_ERR_BAD_ARG;
@@ -54,7 +56,8 @@ KB_EXPORT int kb_attention_decode_mma(const void* q, int q_stride, void* out, in
     if (rc != 0) return rc;
     dim3 grid(num_rows, Hq);
     kb_launch(attention_decode_merge_kernel, dim3(grid), dim3(128), 0, stream, part_o, part_ml, seq_lens, decode_rows, decode_tokens,
-                                                            (__nv_bfloat16*)out, out_stride, Hq, D, window, num_splits);
+                                                            (__nv_bfloat16*)out, out_stride, Hq, D, window, num_splits, sinks,
+                                                            (const __nv_bfloat16*)gate, gate_stride);
     return kb_launch_result();
 }
 

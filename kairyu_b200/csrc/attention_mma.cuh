@@ -200,7 +200,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
                          const int* __restrict__ seq_lens, const int* __restrict__ block_table,
                          int max_pages, const int* __restrict__ tile_rows,
                          const int* __restrict__ tile_starts, int Hq, int Hkv, int D, int page_size,
-                         int num_pages, float scale, int window, int* flag) {
+                         int num_pages, float scale, int window, const float* __restrict__ sinks,
+                         const __nv_bfloat16* __restrict__ gate, int gate_stride, int* flag) {
     pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int STRIDE = Tile<DP>::STRIDE;
@@ -431,6 +432,11 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
         l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
         l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
         l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+        if (sinks) {  // exp(sink) joins the denominator; the scores' maxima are in the base-2 scale
+            const float sk = sinks[h] * LOG2E;
+            l0 += exp2f(sk - m_run[mt][0]);
+            l1 += exp2f(sk - m_run[mt][1]);
+        }
         const float inv0 = l0 > 0.0f ? 1.0f / l0 : 0.0f;
         const float inv1 = l1 > 0.0f ? 1.0f / l1 : 0.0f;
         const int r0 = warp_row0 + mt * 16 + g;
@@ -440,12 +446,22 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
             const int col = dt * 8 + tq * 2;
             if (col < D) {
                 if (r0 < rows_here) {
-                    __nv_bfloat162 v = __floats2bfloat162_rn(o[mt][dt][0] * inv0, o[mt][dt][1] * inv0);
-                    *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(tok0 + q0 + r0) * out_stride + (size_t)h * D + col) = v;
+                    float a = o[mt][dt][0] * inv0, b = o[mt][dt][1] * inv0;
+                    if (gate) {  // the output gate: sigmoid of the gate's columns of this token and head, in 32-bit
+                        const float2 gv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gate + (size_t)(tok0 + q0 + r0) * gate_stride + (size_t)h * D + col));
+                        a *= 1.0f / (1.0f + __expf(-gv.x));
+                        b *= 1.0f / (1.0f + __expf(-gv.y));
+                    }
+                    *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(tok0 + q0 + r0) * out_stride + (size_t)h * D + col) = __floats2bfloat162_rn(a, b);
                 }
                 if (r1 < rows_here) {
-                    __nv_bfloat162 v = __floats2bfloat162_rn(o[mt][dt][2] * inv1, o[mt][dt][3] * inv1);
-                    *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(tok0 + q0 + r1) * out_stride + (size_t)h * D + col) = v;
+                    float a = o[mt][dt][2] * inv1, b = o[mt][dt][3] * inv1;
+                    if (gate) {
+                        const float2 gv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gate + (size_t)(tok0 + q0 + r1) * gate_stride + (size_t)h * D + col));
+                        a *= 1.0f / (1.0f + __expf(-gv.x));
+                        b *= 1.0f / (1.0f + __expf(-gv.y));
+                    }
+                    *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(tok0 + q0 + r1) * out_stride + (size_t)h * D + col) = __floats2bfloat162_rn(a, b);
                 }
             }
         }
@@ -708,7 +724,8 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o,
                                               const int* __restrict__ decode_rows,
                                               const int* __restrict__ decode_tokens,
                                               __nv_bfloat16* __restrict__ out, int out_stride, int Hq,
-                                              int D, int window, int num_splits) {
+                                              int D, int window, int num_splits, const float* __restrict__ sinks,
+                                              const __nv_bfloat16* __restrict__ gate, int gate_stride) {
     pdl_wait();
     const int slot = blockIdx.x;
     const int h = blockIdx.y;
@@ -722,15 +739,18 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o,
     const size_t base = ((size_t)slot * Hq + h) * num_splits;
     float big = -INFINITY;
     for (int s = first; s <= last; ++s) big = fmaxf(big, part_ml[(base + s) * 2]);
+    const float sink_term = sinks ? exp2f(sinks[h] * LOG2E - big) : 0.0f;  // exp(sink) joins the denominator, once
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float acc = 0.0f, den = 0.0f;
+        float acc = 0.0f, den = sink_term;
         for (int s = first; s <= last; ++s) {
             const float ms = part_ml[(base + s) * 2];
             const float f = ms == -INFINITY ? 0.0f : exp2f(ms - big);
             acc += part_o[(base + s) * D + d] * f;
             den += part_ml[(base + s) * 2 + 1] * f;
         }
-        out[(size_t)token * out_stride + (size_t)h * D + d] = __float2bfloat16_rn(den > 0.0f ? acc / den : 0.0f);
+        float result = den > 0.0f ? acc / den : 0.0f;
+        if (gate) result *= 1.0f / (1.0f + __expf(-__bfloat162float(gate[(size_t)token * gate_stride + (size_t)h * D + d])));  // the output gate
+        out[(size_t)token * out_stride + (size_t)h * D + d] = __float2bfloat16_rn(result);
     }
 }
 
@@ -764,14 +784,14 @@ static int launch_prefill(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* o
                           const int* qo_indptr, const int* seq_lens, const int* block_table,
                           int max_pages, const int* tile_rows, const int* tile_starts, int num_tiles,
                           int Hq, int Hkv, int D, int page_size, int num_pages, float scale,
-                          int window, int* flag, cudaStream_t stream) {
+                          int window, const float* sinks, const __nv_bfloat16* gate, int gate_stride, int* flag, cudaStream_t stream) {
     const size_t smem = prefill_smem<DP, MT>();
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DP, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid(Hq, num_tiles);
     kb_launch(attention_prefill_kernel<DP, MT>, dim3(grid), dim3(MMA_THREADS), smem, stream, 
         q, q_stride, out, out_stride, k_cache, v_cache, qo_indptr, seq_lens, block_table, max_pages,
-        tile_rows, tile_starts, Hq, Hkv, D, page_size, num_pages, scale, window, flag);
+        tile_rows, tile_starts, Hq, Hkv, D, page_size, num_pages, scale, window, sinks, gate, gate_stride, flag);
     return kb_launch_result();
 }
 

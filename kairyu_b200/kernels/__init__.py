@@ -598,7 +598,7 @@ def diff_attention_mma(
         launch(ctx.decode_rows, ctx.decode_tokens, ctx.num_decode_rows, 1)
 
 
-ATTENTION_MMA_SINKS = False  # whether the tensor-core attention kernels take sink logits; until they do, the 32-bit-arithmetic kernel runs
+ATTENTION_MMA_SINKS = True  # the tensor-core attention kernels take sink logits (the mma.sync pair does; with sinks the TMA-fed kernels are passed by)
 
 DECODE_SPLIT = 128  # keys per split of the split-KV kernel (csrc/attention_mma.cu: DEC_SPLIT)
 
@@ -625,6 +625,17 @@ def attention_prefill_wide_tile_rows(head_dim: int) -> Optional[int]:
     that walks two 128-query tiles a block, csrc/attention_prefill_tc5.cu), or None for head sizes
     it does not cover."""
     return 256 if head_dim == 128 else None
+
+
+def _check_sinks(what: str, num_q_heads: int, sinks: Optional[torch.Tensor]) -> None:
+    if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != num_q_heads or not sinks.is_contiguous()):
+        raise KernelError(f"{what}: sinks must be contiguous fp32, one a query head")
+
+
+def _check_mma_gate(what: str, q: torch.Tensor, gate: Optional[torch.Tensor]) -> None:
+    if gate is not None and (gate.dtype != torch.bfloat16 or gate.dim() != 2 or gate.shape[0] != q.shape[0] or gate.stride(1) != 1
+                             or gate.data_ptr() % 4 or gate.stride(0) % 2):
+        raise KernelError(f"{what}: the gate must be bf16, a row a token, inner stride 1, rows aligned to 4 bytes")
 
 
 def _check_mma_common(what: str, q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor) -> None:
@@ -659,6 +670,8 @@ def attention_prefill_mma(
     num_splits: Optional[int] = None,
     wide_tiles: Optional[tuple[int, torch.Tensor, torch.Tensor]] = None,
     two_tiles: Optional[bool] = None,
+    sinks: Optional[torch.Tensor] = None,
+    gate: Optional[torch.Tensor] = None,
 ) -> None:
     """Flash attention over query tiles (``attention_prefill_tile_rows`` queries each) of
     rows with several tokens (bf16).
@@ -670,15 +683,20 @@ def attention_prefill_mma(
 
     ``wide_tiles`` (count, rows, starts of tiles of ``attention_prefill_wide_tile_rows`` queries over the
     same portions): long portions of head size 128 go to the kernel that takes two query tiles a block
-    when its grid makes two waves or more; ``two_tiles`` overrides that choice (tests)."""
+    when its grid makes two waves or more; ``two_tiles`` overrides that choice (tests).
+
+    ``sinks``: fp32 [heads], a logit a head whose exp joins the softmax's denominator.  ``gate``: bf16 [tokens, >= heads *
+    head_dim], columns laid out as ``out``'s; the result is multiplied by its sigmoid.  The mma.sync kernel takes both."""
     what = "attention_prefill_mma"
-    _need_cuda(what, q, out, k_cache, v_cache, qo_indptr, seq_lens, block_table, tile_rows, tile_starts)
+    _need_cuda(what, q, out, k_cache, v_cache, qo_indptr, seq_lens, block_table, tile_rows, tile_starts, sinks, gate)
+    _check_sinks(what, num_q_heads, sinks)
+    _check_mma_gate(what, q, gate)
     _need_i32(what, qo_indptr, seq_lens, block_table, tile_rows, tile_starts)
     _check_mma_common(what, q, out, k_cache, v_cache)
     num_pages, page_size, num_kv_heads, head_dim = k_cache.shape
     if not attention_mma_supported(head_dim, num_q_heads, num_kv_heads):
         raise KernelError(f"{what}: head_dim {head_dim} with {num_q_heads}/{num_kv_heads} heads is not supported")
-    if _prefill_tc5_ok(q, out, k_cache, v_cache):  # tcgen05 + TMA: S and O in tensor memory
+    if sinks is None and gate is None and _prefill_tc5_ok(q, out, k_cache, v_cache):  # tcgen05 + TMA: S and O in tensor memory
         fn = _fn(
             "attention_prefill_tc5",
             "kb_attention_prefill_tc5",
@@ -723,14 +741,14 @@ def attention_prefill_mma(
     fn = _fn(
         "attention_mma",
         "kb_attention_prefill_mma",
-        [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+        [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
     )
     _check(
         fn(
             q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
             qo_indptr.data_ptr(), seq_lens.data_ptr(), block_table.data_ptr(), block_table.shape[1],
             tile_rows.data_ptr(), tile_starts.data_ptr(), int(num_tiles), num_q_heads, num_kv_heads, head_dim,
-            page_size, num_pages, float(scale), int(window), _ptr(flag), _stream(),
+            page_size, num_pages, float(scale), int(window), _ptr(sinks), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(flag), _stream(),
         ),
         what,
     )
@@ -754,21 +772,28 @@ def attention_decode_mma(
     workspace: object,
     flag: Optional[torch.Tensor] = None,
     num_splits: Optional[int] = None,
+    sinks: Optional[torch.Tensor] = None,
+    gate: Optional[torch.Tensor] = None,
 ) -> None:
     """Split-KV attention of rows that carry one token (bf16), then the merge.
+
+    ``sinks``: fp32 [heads], a logit a head whose exp joins the softmax's denominator in the merge.  ``gate``: bf16 [tokens, >=
+    heads * head_dim]; the merge multiplies the result by its sigmoid.  The mma.sync kernel takes both.
 
     ``max_seq_len`` bounds every row's length; it sizes the grid and the scratch
     (``workspace.flat`` gives persistent fp32 buffers).  ``num_splits`` overrides the
     number of splits of the TMA-fed kernel (tests use it to make a block stream many tiles).
     """
     what = "attention_decode_mma"
-    _need_cuda(what, q, out, k_cache, v_cache, seq_lens, block_table, decode_rows, decode_tokens)
+    _need_cuda(what, q, out, k_cache, v_cache, seq_lens, block_table, decode_rows, decode_tokens, sinks, gate)
+    _check_sinks(what, num_q_heads, sinks)
+    _check_mma_gate(what, q, gate)
     _need_i32(what, seq_lens, block_table, decode_rows, decode_tokens)
     _check_mma_common(what, q, out, k_cache, v_cache)
     num_pages, page_size, num_kv_heads, head_dim = k_cache.shape
     if not attention_mma_supported(head_dim, num_q_heads, num_kv_heads):
         raise KernelError(f"{what}: head_dim {head_dim} with {num_q_heads}/{num_kv_heads} heads is not supported")
-    if _decode_tma_ok(k_cache, v_cache):  # tiled TMA copies of whole runs of key rows, streamed through a ring
+    if sinks is None and gate is None and _decode_tma_ok(k_cache, v_cache):  # tiled TMA copies of whole runs of key rows, streamed through a ring
         splits_fn = _fn("attention_decode_tma", "kb_attention_decode_tma_splits", [c_int, c_int, c_int, c_int])
         if num_splits is None:
             num_splits = splits_fn(int(num_rows), num_kv_heads, head_dim, max(1, int(max_seq_len)))
@@ -801,14 +826,15 @@ def attention_decode_mma(
     fn = _fn(
         "attention_mma",
         "kb_attention_decode_mma",
-        [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+        [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
     )
     _check(
         fn(
             q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
             seq_lens.data_ptr(), block_table.data_ptr(), block_table.shape[1], decode_rows.data_ptr(),
             decode_tokens.data_ptr(), int(num_rows), num_q_heads, num_kv_heads, head_dim, page_size, num_pages,
-            float(scale), int(window), num_splits, part_o.data_ptr(), part_ml.data_ptr(), _ptr(flag), _stream(),
+            float(scale), int(window), num_splits, part_o.data_ptr(), part_ml.data_ptr(), _ptr(sinks), _ptr(gate),
+            gate.stride(0) if gate is not None else 0, _ptr(flag), _stream(),
         ),
         what,
         launches=2,

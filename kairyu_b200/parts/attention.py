@@ -63,12 +63,14 @@ def run_paged_attention(
     window: int,
     sinks: Optional[torch.Tensor] = None,
     value_dim: Optional[int] = None,
+    gate: Optional[torch.Tensor] = None,
 ) -> None:
     """Attention of every token of the step; picks the kernels for the dtype.
 
     ``sinks`` (fp32, one logit a query head) joins every softmax's denominator.  ``value_dim``: a value
     is the first ``value_dim`` columns of its row (for a cache whose rows serve as keys and values);
     ``out`` keeps ``head_dim`` columns a head either way, of which the first ``value_dim`` are the result.
+    ``gate`` ([tokens, heads * head_dim], the tensor-core kernels only): the result is multiplied by its sigmoid.
 
     float32: the fp32 kernel for all tokens (its arithmetic per token does not
     depend on the batch).  bfloat16: tensor-core kernels, query tiles for
@@ -83,6 +85,8 @@ def run_paged_attention(
         and (sinks is None or kernels.ATTENTION_MMA_SINKS)
     )
     if not use_mma:
+        if gate is not None:
+            raise ValueError("run_paged_attention: the 32-bit-arithmetic kernel takes no gate")
         kernels.paged_attention_generic(
             qkv,
             out,
@@ -129,6 +133,8 @@ def run_paged_attention(
             max_seq_len=ctx.max_portion_seq_len,
             workspace=ctx.workspace,
             wide_tiles=ctx.tiles.get(kernels.attention_prefill_wide_tile_rows(head_dim)),
+            sinks=sinks,
+            gate=gate,
         )
     if ctx.num_decode_rows:
         with torch.cuda.stream(beside.stream) if beside is not None else contextlib.nullcontext():
@@ -148,6 +154,8 @@ def run_paged_attention(
                 window=window,
                 workspace=ctx.workspace,
                 flag=ctx.error_flag,
+                sinks=sinks,
+                gate=gate,
             )
             if beside is not None:
                 beside.join.record()

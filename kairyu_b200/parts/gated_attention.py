@@ -15,6 +15,9 @@ One product gives ``q | k | v | g`` (``g``: the gate's rows, ``num_heads * value
 The gate reads the mixer's input, as the projections do.  Query head h uses key/value head
 ``h // (num_heads / num_kv_heads)``.  Cached per token and key/value head: the normed, rotated key (``head_dim``) and the
 value (``value_dim``).  Norm statistics, the rotation, scores, softmax and the gate are 32-bit in both modes.
+bfloat16 with ``head_dim == value_dim`` of a size the paged tensor-core kernels take runs on them (prompt portions in query
+tiles, single tokens split over the keys), the sink in their last step and the gate at their store; everything else runs the
+32-bit-arithmetic kernel.
 
 Tensors under ``prefix``: ``q``, ``k``, ``v``, ``o``, and ``g``, ``q.norm``, ``k.norm``, ``sink`` as the options ask.
 """
@@ -26,6 +29,7 @@ from typing import Any, Mapping, Optional
 import torch
 
 from kairyu_b200 import kernels
+from kairyu_b200.parts.attention import run_paged_attention
 from kairyu_b200.parts.base import MIXERS, POSITION_ENCODINGS, CacheView, Mixer, PagedKVSpec, PartSpec, StepContext, TensorSpec
 
 
@@ -142,10 +146,17 @@ class GatedAttention(Mixer):
         return (PagedKVSpec(self.num_kv_heads, self.head_dim, self.window, v_head_dim=self.value_dim),)
 
     def _tensor_cores(self) -> bool:
-        return self.dtype == torch.bfloat16 and kernels.diff_attention_mma_supported(self.head_dim, self.value_dim, self.num_heads, self.num_kv_heads, maps=1)
+        """bfloat16 with keys and values of one width: the paged tensor-core kernels (sink and gate in their last
+        steps).  Other widths and float32 take the 32-bit-arithmetic kernel."""
+        return (self.dtype == torch.bfloat16 and self.head_dim == self.value_dim
+                and kernels.attention_mma_supported(self.head_dim, self.num_heads, self.num_kv_heads)
+                and (self.sink is None or kernels.ATTENTION_MMA_SINKS))
 
     def query_tile_sizes(self) -> tuple[int, ...]:
-        return (kernels.DIFF_ATTENTION_TILE,) if self._tensor_cores() else ()
+        if not self._tensor_cores():
+            return ()
+        wide = kernels.attention_prefill_wide_tile_rows(self.head_dim)
+        return (kernels.attention_prefill_tile_rows(self.head_dim),) + ((wide,) if wide else ())
 
     # -- compute
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
@@ -165,15 +176,14 @@ class GatedAttention(Mixer):
             flag=ctx.error_flag,
         )
         mixed = ws.buffer("gattn.mixed", tokens, self.out_size, self.dtype)
-        constants = dict(
-            num_q_heads=self.num_heads, maps=1, scale=self.scale, window=self.window or 0, sinks=self.sinks,
-            gate=packed[:, self.g_offset :] if self.gate else None, flag=ctx.error_flag,
-        )
+        gate = packed[:, self.g_offset :] if self.gate else None
         if self._tensor_cores() and not ctx.extras.get("force_generic_attention", False):
-            kernels.diff_attention_mma(packed, mixed, cache.k, cache.v, ctx=ctx, block_table=block_table, **constants)
+            run_paged_attention(packed, mixed, cache, ctx, num_q_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
+                                scale=self.scale, window=self.window or 0, sinks=self.sinks, gate=gate)
         else:
             kernels.diff_attention_generic(
-                packed, mixed, cache.k, cache.v, positions=ctx.positions, row_ids=ctx.row_ids, block_table=block_table, **constants
+                packed, mixed, cache.k, cache.v, positions=ctx.positions, row_ids=ctx.row_ids, block_table=block_table,
+                num_q_heads=self.num_heads, maps=1, scale=self.scale, window=self.window or 0, sinks=self.sinks, gate=gate, flag=ctx.error_flag,
             )
         out = ws.buffer("gattn.out", tokens, self.hidden_size, self.dtype)
         kernels.linear(mixed, self.w_o, None, out)
