@@ -624,17 +624,16 @@ def main() -> int:
     parser.add_argument("--prompt-len", type=int, default=None, help="another prompt length than the shape's (with --gen-len, within the context length)")
     parser.add_argument("--gen-len", type=int, default=None)
     parser.add_argument("--context-len", type=int, default=None, help="another context length than the shape's (longer prompts)")
-    parser.add_argument("--design", choices=["makilorn", "karesun"], default=None,
-                        help="instead of the default workload: this design's prefill and decode throughput at a few layer sizes beside the dense decoder of equal size")
+    parser.add_argument("--design", choices=["makilorn", "karesun", "mapalorn"], default=None,
+                        help="instead of the default workload: this design's prefill and decode throughput at a few layer sizes beside the closest other model of equal size")
     args = parser.parse_args()
     if args.design is not None:
         if args.gpus != 1:
             print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
             return 2
-        import bench_karesun
-        import bench_makilorn
+        import importlib
 
-        return (bench_makilorn if args.design == "makilorn" else bench_karesun).run(args)
+        return importlib.import_module(f"bench_{args.design}").run(args)
     if SHAPES[args.shape] is not None:
         shape = SHAPES[args.shape]
         MODEL, MODEL_NAME, SEED = shape["model"], shape["name"], shape["seed"]

@@ -118,7 +118,8 @@ attention_decode_tma_body(const CUtensorMap& map_k, const CUtensorMap& map_v,
                           const int* __restrict__ block_table, int max_pages, const int* __restrict__ decode_rows,
                           const int* __restrict__ decode_tokens, int Hq, int Hkv, int page_size, int page_shift,
                           int num_pages, float scale, int window, int num_splits, float* __restrict__ part_o,
-                          float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out, int out_stride, int combine, int* flag) {
+                          float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out, int out_stride, int combine,
+                          const float* __restrict__ sinks, const __nv_bfloat16* __restrict__ gate, int gate_stride, int* flag) {
     using S = TmaSmem<D, ST>;
     constexpr int HALVES = S::HALVES;
     static_assert(!JOINED || HALVES == 1, "keys and values share a copy at head_dim 64 only");
@@ -404,7 +405,11 @@ attention_decode_tma_body(const CUtensorMap& map_k, const CUtensorMap& map_v,
             den += sL[w * 16 + r] * f;
         }
         if (combine == COMBINE_DIRECT) {  // the only split of its row: what the merge kernel would make of it
-            out[(size_t)token * out_stride + (size_t)(kvh * G + r) * D + d] = __float2bfloat16_rn(den > 0.0f ? acc / den : 0.0f);
+            const size_t column = (size_t)(kvh * G + r) * D + d;
+            if (sinks && big != -INFINITY) den += exp2f(sinks[kvh * G + r] * LOG2E - big);  // exp(sink) joins the denominator, once
+            float result = den > 0.0f ? acc / den : 0.0f;
+            if (gate) result *= 1.0f / (1.0f + __expf(-__bfloat162float(gate[(size_t)token * gate_stride + column])));  // the output gate
+            out[(size_t)token * out_stride + column] = __float2bfloat16_rn(result);
             continue;
         }
         const size_t pidx = ((size_t)slot * Hq + (kvh * G + r)) * num_splits + split;
@@ -421,10 +426,11 @@ attention_decode_tma_body(const CUtensorMap& map_k, const CUtensorMap& map_v,
         int q_stride, const int* __restrict__ seq_lens, const int* __restrict__ block_table, int max_pages,                  \
         const int* __restrict__ decode_rows, const int* __restrict__ decode_tokens, int Hq, int Hkv, int page_size,          \
         int page_shift, int num_pages, float scale, int window, int num_splits, float* __restrict__ part_o,                  \
-        float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out, int out_stride, int combine, int* flag
+        float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out, int out_stride, int combine,                         \
+        const float* __restrict__ sinks, const __nv_bfloat16* __restrict__ gate, int gate_stride, int* flag
 #define DECODE_TMA_ARGS                                                                                                     \
     map_k, map_v, q, q_stride, seq_lens, block_table, max_pages, decode_rows, decode_tokens, Hq, Hkv, page_size, page_shift, \
-        num_pages, scale, window, num_splits, part_o, part_ml, out, out_stride, combine, flag
+        num_pages, scale, window, num_splits, part_o, part_ml, out, out_stride, combine, sinks, gate, gate_stride, flag
 
 template <int D, bool JOINED, int ST>
 __global__ void __launch_bounds__(TMA_THREADS) attention_decode_tma_kernel(DECODE_TMA_PARAMS) {
@@ -440,7 +446,9 @@ __global__ void __launch_bounds__(TMA_THREADS, 3) attention_decode_tma_kernel<12
 __global__ void attention_decode_tma_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                   const int* __restrict__ seq_lens, const int* __restrict__ decode_rows,
                                                   const int* __restrict__ decode_tokens, __nv_bfloat16* __restrict__ out,
-                                                  int out_stride, int Hq, int D, int window, int num_splits) {
+                                                  int out_stride, int Hq, int D, int window, int num_splits,
+                                                  const float* __restrict__ sinks, const __nv_bfloat16* __restrict__ gate,
+                                                  int gate_stride) {
     pdl_trigger();  // the product after this one may fetch its first weights meanwhile
     // rows and lengths come from the host's copy of the step: looked up ahead of the wait for the partial results
     const int slot = blockIdx.x;
@@ -458,15 +466,18 @@ __global__ void attention_decode_tma_merge_kernel(const float* __restrict__ part
     pdl_wait();
     float big = -INFINITY;
     for (int s = 0; s < used; ++s) big = fmaxf(big, part_ml[(base + s) * 2]);
+    const float sink_term = sinks && big != -INFINITY ? exp2f(sinks[h] * LOG2E - big) : 0.0f;  // exp(sink) joins the denominator, once
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float acc = 0.0f, den = 0.0f;
+        float acc = 0.0f, den = sink_term;
         for (int s = 0; s < used; ++s) {
             const float ms = part_ml[(base + s) * 2];
             const float f = ms == -INFINITY ? 0.0f : exp2f(ms - big);
             acc += part_o[(base + s) * D + d] * f;
             den += part_ml[(base + s) * 2 + 1] * f;
         }
-        out[(size_t)token * out_stride + (size_t)h * D + d] = __float2bfloat16_rn(den > 0.0f ? acc / den : 0.0f);
+        float result = den > 0.0f ? acc / den : 0.0f;
+        if (gate) result *= 1.0f / (1.0f + __expf(-__bfloat162float(gate[(size_t)token * gate_stride + (size_t)h * D + d])));  // the output gate
+        out[(size_t)token * out_stride + (size_t)h * D + d] = __float2bfloat16_rn(result);
     }
 }
 
@@ -547,7 +558,8 @@ template <int D, bool JOINED, int ST = TmaStages<D>::value>
 int launch(const CUtensorMap* mk, const CUtensorMap* mv, const __nv_bfloat16* q, int q_stride, const int* seq_lens,
            const int* block_table, int max_pages, const int* decode_rows, const int* decode_tokens, int num_rows, int Hq,
            int Hkv, int page_size, int num_pages, float scale, int window, int num_splits, float* part_o, float* part_ml,
-           __nv_bfloat16* out, int out_stride, int combine, int* flag, cudaStream_t stream) {
+           __nv_bfloat16* out, int out_stride, int combine, const float* sinks, const __nv_bfloat16* gate, int gate_stride, int* flag,
+           cudaStream_t stream) {
     const size_t smem = TmaSmem<D, ST>::TOTAL;
     cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<D, JOINED, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -556,7 +568,7 @@ int launch(const CUtensorMap* mk, const CUtensorMap* mv, const __nv_bfloat16* q,
     dim3 grid(num_rows, Hkv, num_splits);
     kb_launch(attention_decode_tma_kernel<D, JOINED, ST>, dim3(grid), dim3(TMA_THREADS), smem, stream, *mk, *mv, q, q_stride, seq_lens,
               block_table, max_pages, decode_rows, decode_tokens, Hq, Hkv, page_size, shift, num_pages, scale,
-              window, num_splits, part_o, part_ml, out, out_stride, combine, flag);
+              window, num_splits, part_o, part_ml, out, out_stride, combine, sinks, gate, gate_stride, flag);
     return kb_launch_result();
 }
 
@@ -663,12 +675,14 @@ KB_EXPORT int kb_attention_encode_joined_map(void* map_out, const void* base_k, 
 // `joined` (head_dim 64 only), map_k is a map of kb_attention_encode_joined_map and map_v is not read.
 // num_splits: any value from 1 up (kb_attention_decode_tma_splits gives a good one).
 // part_o: [rows, Hq, splits, D] fp32; part_ml: [rows, Hq, splits, 2] fp32 (scratch; only read
-// and written with more than one split).
+// and written with more than one split).  sinks (optional): one fp32 logit a query head whose exp joins the
+// softmax's denominator; gate (optional): bf16 [tokens, gate_stride] laid out as out, by whose sigmoid the result
+// is multiplied.  Both act where a row's result is divided: in the kernel with one split, in the merge kernel else.
 KB_EXPORT int kb_attention_decode_tma(const void* map_k, const void* map_v, const void* q, int q_stride, void* out, int out_stride,
                                       const int* seq_lens, const int* block_table, int max_pages, const int* decode_rows,
                                       const int* decode_tokens, int num_rows, int Hq, int Hkv, int D, int page_size, int num_pages,
-                                      float scale, int window, int num_splits, float* part_o, float* part_ml, int joined, int* flag,
-                                      cudaStream_t stream) {
+                                      float scale, int window, int num_splits, float* part_o, float* part_ml, int joined,
+                                      const float* sinks, const void* gate, int gate_stride, int* flag, cudaStream_t stream) {
     if (num_rows == 0) return 0;
     if (joined && D != 64) return KB_ERR_UNSUPPORTED_SIZE;
     if (joined) map_v = map_k;
@@ -683,7 +697,8 @@ KB_EXPORT int kb_attention_decode_tma(const void* map_k, const void* map_v, cons
     const CUtensorMap* mv = (const CUtensorMap*)map_v;
     int rc;
 #define ARGS mk, mv, (const __nv_bfloat16*)q, q_stride, seq_lens, block_table, max_pages, decode_rows, decode_tokens, num_rows, Hq, \
-             Hkv, page_size, num_pages, scale, window, num_splits, part_o, part_ml, (__nv_bfloat16*)out, out_stride, combine, flag, stream
+             Hkv, page_size, num_pages, scale, window, num_splits, part_o, part_ml, (__nv_bfloat16*)out, out_stride, combine, sinks,    \
+             (const __nv_bfloat16*)gate, gate_stride, flag, stream
     switch (D) {
         case 64: {
             // a grid that four-stage blocks cannot hold at once runs with three stages, four blocks an SM
@@ -705,7 +720,7 @@ KB_EXPORT int kb_attention_decode_tma(const void* map_k, const void* map_v, cons
     if (rc != 0 || combine != COMBINE_SCRATCH) return rc;
     dim3 grid(num_rows, Hq);
     kb_launch(attention_decode_tma_merge_kernel, dim3(grid), dim3(128), 0, stream, part_o, part_ml, seq_lens, decode_rows,
-              decode_tokens, (__nv_bfloat16*)out, out_stride, Hq, D, window, num_splits);
+              decode_tokens, (__nv_bfloat16*)out, out_stride, Hq, D, window, num_splits, sinks, (const __nv_bfloat16*)gate, gate_stride);
     return kb_launch_result();
 }
 

@@ -55,6 +55,20 @@
 #define FA_BN 64
 #define FA_STAGES 2
 #define FA_LOG2E 1.4426950408889634f
+
+// The last steps an attention variant may add: `sinks` (one fp32 logit a query head; exp(sink) joins the row's
+// denominator, which here is kept relative to 2^m_ref) and `gate` (bf16 [tokens, gate_stride], columns laid out as
+// out's; the result is multiplied by its sigmoid, in 32-bit, before the one rounding at the store).
+__device__ __forceinline__ void fa_gate8(const __nv_bfloat16* gate_at, float (&factor)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(gate_at);
+    const __nv_bfloat162* two = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float2 g = __bfloat1622float2(two[e]);
+        factor[2 * e] = 1.0f / (1.0f + __expf(-g.x));
+        factor[2 * e + 1] = 1.0f / (1.0f + __expf(-g.y));
+    }
+}
 #define FA_RESCALE_STEP 8.0f
 #define KB_FLAG_MISALIGNED 32
 #define KB_FLAG_TIMEOUT_PREFILL 128  // this kernel's own bit, beside the common KB_FLAG_TIMEOUT
@@ -110,7 +124,8 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                              const int* __restrict__ block_table, int max_pages, const int* __restrict__ tile_rows,
                              const int* __restrict__ tile_starts, int num_tiles, int Hq, int Hkv, int page_size, int page_shift,
                              int num_pages, float scale, int window, int merged, int paired, int splits, float* __restrict__ part_o,
-                             float* __restrict__ part_ml, int* flag) {
+                             float* __restrict__ part_ml, const float* __restrict__ sinks, const __nv_bfloat16* __restrict__ gate,
+                             int gate_stride, int* flag) {
     using Cfg = FaCfg<D>;
     constexpr int BANDS = Cfg::BANDS;
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -510,8 +525,10 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 g0 += num_kt;
                 continue;
             }
+            if (sinks && m_ref != -INFINITY) l += exp2f(sinks[h] * FA_LOG2E - m_ref);
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             __nv_bfloat16* dst = out + (size_t)(t.tok0 + t.q0 + r) * out_stride + (size_t)h * D;
+            const __nv_bfloat16* gate_row = gate && valid ? gate + (size_t)(t.tok0 + t.q0 + r) * gate_stride + (size_t)h * D : nullptr;
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
                 uint32_t o[32];
@@ -521,10 +538,17 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         uint32_t w[4];
+                        float by[8] = {inv, inv, inv, inv, inv, inv, inv, inv};
+                        if (gate_row) {
+                            float factor[8];
+                            fa_gate8(gate_row + c * 32 + i * 8, factor);
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) by[e] *= factor[e];
+                        }
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(o[8 * i + 2 * e]) * inv,
-                                                                        __uint_as_float(o[8 * i + 2 * e + 1]) * inv);
+                            __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(o[8 * i + 2 * e]) * by[2 * e],
+                                                                        __uint_as_float(o[8 * i + 2 * e + 1]) * by[2 * e + 1]);
                             w[e] = *reinterpret_cast<uint32_t*>(&pair);
                         }
                         *reinterpret_cast<uint4*>(dst + c * 32 + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -593,7 +617,8 @@ attention_prefill_tc5_two_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                  const int* __restrict__ qo_indptr, const int* __restrict__ seq_lens,
                                  const int* __restrict__ block_table, int max_pages, const int* __restrict__ tile_rows,
                                  const int* __restrict__ tile_starts, int num_tiles, int Hq, int Hkv, int page_size, int page_shift,
-                                 int num_pages, float scale, int window, int merged, int* flag) {
+                                 int num_pages, float scale, int window, int merged, const float* __restrict__ sinks,
+                                 const __nv_bfloat16* __restrict__ gate, int gate_stride, int* flag) {
     using Cfg = FbCfg;
     constexpr int D = Cfg::D;
     constexpr int BANDS = Cfg::BANDS;
@@ -935,8 +960,10 @@ attention_prefill_tc5_two_kernel(const __grid_constant__ CUtensorMap map_q, cons
             if (ok && !mbar_wait(o_done + x, 0, abort_word)) ok = false;
             if (ok) {
                 tc_fence_after();
+                if (sinks && m_ref != -INFINITY) l += exp2f(sinks[h] * FA_LOG2E - m_ref);
                 const float inv = l > 0.0f ? 1.0f / l : 0.0f;
                 __nv_bfloat16* dst = out + (size_t)(tok0 + q0 + x * FA_BM + r) * out_stride + (size_t)h * D;
+                const __nv_bfloat16* gate_row = gate && valid ? gate + (size_t)(tok0 + q0 + x * FA_BM + r) * gate_stride + (size_t)h * D : nullptr;
 #pragma unroll
                 for (int c = 0; c < D / 32; ++c) {
                     uint32_t o[32];
@@ -946,10 +973,17 @@ attention_prefill_tc5_two_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
                             uint32_t w[4];
+                            float by[8] = {inv, inv, inv, inv, inv, inv, inv, inv};
+                            if (gate_row) {
+                                float factor[8];
+                                fa_gate8(gate_row + c * 32 + q * 8, factor);
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) by[e] *= factor[e];
+                            }
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
-                                __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(o[8 * q + 2 * e]) * inv,
-                                                                            __uint_as_float(o[8 * q + 2 * e + 1]) * inv);
+                                __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(o[8 * q + 2 * e]) * by[2 * e],
+                                                                            __uint_as_float(o[8 * q + 2 * e + 1]) * by[2 * e + 1]);
                                 w[e] = *reinterpret_cast<uint32_t*>(&pair);
                             }
                             *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -987,7 +1021,8 @@ template <int D>
 __global__ void attention_prefill_tc5_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                    const int* __restrict__ qo_indptr, const int* __restrict__ tile_rows,
                                                    const int* __restrict__ tile_starts, int num_tiles, int Hq, int splits,
-                                                   __nv_bfloat16* __restrict__ out, int out_stride) {
+                                                   __nv_bfloat16* __restrict__ out, int out_stride, const float* __restrict__ sinks,
+                                                   const __nv_bfloat16* __restrict__ gate, int gate_stride) {
     constexpr int PER = D / 32;
     pdl_trigger();
     const int lane = threadIdx.x & 31;
@@ -1022,8 +1057,14 @@ __global__ void attention_prefill_tc5_merge_kernel(const float* __restrict__ par
 #pragma unroll
         for (int i = 0; i < PER; ++i) acc[i] += part[i] * f;
     }
+    if (sinks && big != -INFINITY) den += exp2f(sinks[h] * FA_LOG2E - big);
     const float inv = den > 0.0f ? 1.0f / den : 0.0f;
     __nv_bfloat16* dst = out + (size_t)(tok0 + q0 + r) * out_stride + (size_t)h * D + lane * PER;
+    if (gate) {
+        const __nv_bfloat16* gate_at = gate + (size_t)(tok0 + q0 + r) * gate_stride + (size_t)h * D + lane * PER;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) acc[i] *= 1.0f / (1.0f + __expf(-__bfloat162float(gate_at[i])));
+    }
     uint32_t packed[PER / 2];
 #pragma unroll
     for (int i = 0; i < PER; i += 2) {
@@ -1064,7 +1105,8 @@ template <int D>
 static int launch_fa(const CUtensorMap* mq, const CUtensorMap* mk, const CUtensorMap* mv, __nv_bfloat16* out, int out_stride,
                      const int* qo_indptr, const int* seq_lens, const int* block_table, int max_pages, const int* tile_rows,
                      const int* tile_starts, int num_tiles, int Hq, int Hkv, int page_size, int num_pages, float scale, int window,
-                     int merged, int splits, float* part_o, float* part_ml, int* flag, cudaStream_t stream) {
+                     int merged, int splits, float* part_o, float* part_ml, const float* sinks, const __nv_bfloat16* gate, int gate_stride,
+                     int* flag, cudaStream_t stream) {
     const size_t smem = FaCfg<D>::SMEM;
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc5_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -1078,19 +1120,19 @@ static int launch_fa(const CUtensorMap* mq, const CUtensorMap* mk, const CUtenso
     dim3 grid(Hq, paired ? (num_tiles + 1) / 2 : num_tiles, splits);
     kb_launch(attention_prefill_tc5_kernel<D>, dim3(grid), dim3(FA_THREADS), smem, stream, *mq, *mk, *mv, out, out_stride, qo_indptr,
               seq_lens, block_table, max_pages, tile_rows, tile_starts, num_tiles, Hq, Hkv, page_size, shift, num_pages, scale, window, merged,
-              paired, splits, part_o, part_ml, flag);
+              paired, splits, part_o, part_ml, sinks, gate, gate_stride, flag);
     int rc = kb_launch_result();
     if (rc != 0 || splits == 1) return rc;
     const long long pairs = (long long)num_tiles * FA_BM * Hq;
     kb_launch(attention_prefill_tc5_merge_kernel<D>, dim3((unsigned)((pairs + 3) / 4)), dim3(128), 0, stream, (const float*)part_o,
-              (const float*)part_ml, qo_indptr, tile_rows, tile_starts, num_tiles, Hq, splits, out, out_stride);
+              (const float*)part_ml, qo_indptr, tile_rows, tile_starts, num_tiles, Hq, splits, out, out_stride, sinks, gate, gate_stride);
     return kb_launch_result();
 }
 
 static int launch_two(const CUtensorMap* mq, const CUtensorMap* mk, const CUtensorMap* mv, __nv_bfloat16* out, int out_stride,
                       const int* qo_indptr, const int* seq_lens, const int* block_table, int max_pages, const int* wide_rows,
                       const int* wide_starts, int num_wide, int Hq, int Hkv, int page_size, int num_pages, float scale, int window,
-                      int merged, int* flag, cudaStream_t stream) {
+                      int merged, const float* sinks, const __nv_bfloat16* gate, int gate_stride, int* flag, cudaStream_t stream) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc5_two_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FbCfg::SMEM);
     if (e != cudaSuccess) return (int)e;
     int shift = 0;
@@ -1098,7 +1140,7 @@ static int launch_two(const CUtensorMap* mq, const CUtensorMap* mk, const CUtens
     dim3 grid(Hq, num_wide);
     kb_launch(attention_prefill_tc5_two_kernel, dim3(grid), dim3(FB_THREADS), FbCfg::SMEM, stream, *mq, *mk, *mv, out, out_stride, qo_indptr,
               seq_lens, block_table, max_pages, wide_rows, wide_starts, num_wide, Hq, Hkv, page_size, shift, num_pages, scale, window, merged,
-              flag);
+              sinks, gate, gate_stride, flag);
     return kb_launch_result();
 }
 
@@ -1135,14 +1177,17 @@ KB_EXPORT int kb_attention_prefill_tc5_merged(int D, int page_size) { return D >
 // part_o [splits, tiles * 128, Hq, D] and part_ml [splits, tiles * 128, Hq, 2] floats hold their results
 // until a second kernel combines them.  two_tiles (what kb_attention_prefill_tc5_two_tiles gives, or 0): the
 // portions go to the kernel that takes two query tiles a block, whose list (wide_rows, wide_starts,
-// num_wide) holds 256 queries per tile.
+// num_wide) holds 256 queries per tile.  sinks (optional): one fp32 logit a query head whose exp joins the
+// softmax's denominator; gate (optional): bf16 [tokens, gate_stride], 16-byte aligned rows laid out as out's, by
+// whose sigmoid the result is multiplied.
 KB_EXPORT int kb_attention_prefill_tc5(const void* map_q, const void* map_k, const void* map_v, void* out, int out_stride,
                                        const int* qo_indptr, const int* seq_lens, const int* block_table, int max_pages,
                                        const int* tile_rows, const int* tile_starts, int num_tiles, int Hq, int Hkv, int D,
                                        int page_size, int num_pages, float scale, int window, int splits, float* part_o,
                                        float* part_ml, const int* wide_rows, const int* wide_starts, int num_wide, int two_tiles,
-                                       int* flag, cudaStream_t stream) {
+                                       const float* sinks, const void* gate, int gate_stride, int* flag, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
+    if (gate && (gate_stride % 8 != 0 || ((uintptr_t)gate % 16) != 0)) return KB_ERR_BAD_ARG;  // 16-byte loads beside the stores
     if (two_tiles && (D != 128 || splits != 1 || !wide_rows || !wide_starts || num_wide < 1 || num_wide > 65535)) return KB_ERR_BAD_ARG;
     if (splits < 1 || splits > 8 || (splits > 1 && (!part_o || !part_ml || ((uintptr_t)part_o % 16) != 0))) return KB_ERR_BAD_ARG;
     if (!map_q || !map_k || !map_v || !out || !qo_indptr || !seq_lens || !block_table || !tile_rows || !tile_starts) return KB_ERR_NULL;
@@ -1151,11 +1196,11 @@ KB_EXPORT int kb_attention_prefill_tc5(const void* map_q, const void* map_k, con
     if (!kb_attention_prefill_tc5_supported(D, page_size)) return KB_ERR_UNSUPPORTED_SIZE;
 #define ARGS (const CUtensorMap*)map_q, (const CUtensorMap*)map_k, (const CUtensorMap*)map_v, (__nv_bfloat16*)out, out_stride, qo_indptr, \
              seq_lens, block_table, max_pages, tile_rows, tile_starts, num_tiles, Hq, Hkv, page_size, num_pages, scale, window,            \
-             kb_attention_prefill_tc5_merged(D, page_size), splits, part_o, part_ml, flag, stream
+             kb_attention_prefill_tc5_merged(D, page_size), splits, part_o, part_ml, sinks, (const __nv_bfloat16*)gate, gate_stride, flag, stream
     if (two_tiles)
         return launch_two((const CUtensorMap*)map_q, (const CUtensorMap*)map_k, (const CUtensorMap*)map_v, (__nv_bfloat16*)out, out_stride,
                           qo_indptr, seq_lens, block_table, max_pages, wide_rows, wide_starts, num_wide, Hq, Hkv, page_size, num_pages, scale,
-                          window, kb_attention_prefill_tc5_merged(D, page_size), flag, stream);
+                          window, kb_attention_prefill_tc5_merged(D, page_size), sinks, (const __nv_bfloat16*)gate, gate_stride, flag, stream);
     if (D == 64) return launch_fa<64>(ARGS);
     return launch_fa<128>(ARGS);
 #undef ARGS

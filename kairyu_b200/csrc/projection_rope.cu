@@ -105,6 +105,145 @@ projection_norm_rope_write_kernel(T* __restrict__ packed, int stride, int k_offs
         for (int i = threadIdx.x; i < Hkv * DV; i += blockDim.x) v_dst[i] = v[i];
 }
 
+// The same on bfloat16 rows whose heads, offsets and rotated parts are whole 16-byte groups: a thread takes eight
+// columns a turn (a group of the first half with its partner group in split halves; four pairs in one group when
+// interleaved), so that a row is read and written in 16-byte accesses.  The arithmetic is the scalar kernel's.
+struct alignas(16) Bf16x8 {
+    __nv_bfloat162 v[4];
+};
+
+template <typename TW>
+__device__ __forceinline__ void load_weights8(const TW* w, int at, float inv, float (&out)[8]) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) out[e] = w ? inv * to_float(w[at + e]) : inv;
+}
+
+__device__ __forceinline__ void unpack8(const Bf16x8& in, float (&out)[8]) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float2 two = __bfloat1622float2(in.v[e]);
+        out[2 * e] = two.x;
+        out[2 * e + 1] = two.y;
+    }
+}
+
+__device__ __forceinline__ Bf16x8 pack8(const float (&in)[8]) {
+    Bf16x8 out;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) out.v[e] = __floats2bfloat162_rn(in[2 * e], in[2 * e + 1]);
+    return out;
+}
+
+template <typename TW>
+__global__ void __launch_bounds__(PR_THREADS)
+projection_norm_rope_write_vec_kernel(__nv_bfloat16* __restrict__ packed, int stride, int k_offset, int v_offset, int Hq, int Hkv, int D,
+                                      int DV, const TW* __restrict__ wq, const TW* __restrict__ wk, float eps,
+                                      const float* __restrict__ cos_table, const float* __restrict__ sin_table, int rot_half, int max_pos,
+                                      int interleaved, const int* __restrict__ positions, const int* __restrict__ row_ids,
+                                      const int* __restrict__ block_table, int max_pages, const int* __restrict__ write_from,
+                                      __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int page_size,
+                                      int num_pages, int num_rows, int* flag) {
+    __shared__ float scratch[32];
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int row = row_ids[t];
+    const bool pos_ok = rot_half == 0 || (pos >= 0 && pos < max_pos);
+    const float* cs = cos_table + (size_t)(pos_ok ? pos : 0) * rot_half;
+    const float* sn = sin_table + (size_t)(pos_ok ? pos : 0) * rot_half;
+    __nv_bfloat16* k_dst = nullptr;
+    __nv_bfloat16* v_dst = nullptr;
+    bool bad_row = false, bad_page = false;
+    if (k_cache) {
+        if (row < 0 || row >= num_rows) {
+            bad_row = true;
+        } else if (!(write_from && pos < write_from[row])) {
+            const int page_index = pos / page_size;
+            const int page = (pos >= 0 && page_index < max_pages) ? block_table[(size_t)row * max_pages + page_index] : -1;
+            if (page < 0 || page >= num_pages) {
+                bad_page = true;
+            } else {
+                const size_t place = (size_t)page * page_size + (pos % page_size);
+                k_dst = k_cache + place * Hkv * D;
+                v_dst = v_cache + place * Hkv * DV;
+            }
+        }
+    }
+    pdl_wait();
+    if (threadIdx.x == 0 && flag) {
+        if (!pos_ok) atomicOr(flag, KB_FLAG_BAD_POS);
+        if (bad_row) atomicOr(flag, KB_FLAG_BAD_ROW);
+        if (bad_page) atomicOr(flag, KB_FLAG_BAD_PAGE);
+    }
+    __nv_bfloat16* q = packed + (size_t)t * stride;
+    __nv_bfloat16* k = q + k_offset;
+    const __nv_bfloat16* v = q + v_offset;
+    float inv_q = 1.0f, inv_k = 1.0f;
+    if (wq) {
+        float sq = 0.0f, sk = 0.0f;
+        float x[8];
+        for (int i = threadIdx.x; i < Hq * D / 8; i += blockDim.x) {
+            unpack8(*reinterpret_cast<const Bf16x8*>(q + i * 8), x);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sq += x[e] * x[e];
+        }
+        for (int i = threadIdx.x; i < Hkv * D / 8; i += blockDim.x) {
+            unpack8(*reinterpret_cast<const Bf16x8*>(k + i * 8), x);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sk += x[e] * x[e];
+        }
+        inv_q = rsqrtf(block_sum(sq, scratch) / (float)(Hq * D) + eps);
+        inv_k = rsqrtf(block_sum(sk, scratch) / (float)(Hkv * D) + eps);
+    }
+    const int groups = D / 8;                               // 16-byte groups a head
+    const int rot_groups = interleaved ? rot_half / 4 : rot_half / 8;  // groups that begin a rotation (split halves: of the first half)
+    const int skip_from = interleaved ? groups : rot_groups, skip_to = interleaved ? groups : 2 * rot_groups;  // partner groups, done with their first
+    for (int u = threadIdx.x; u < (Hq + Hkv) * groups; u += blockDim.x) {
+        const int head = u / groups, j = u % groups;
+        if (j >= skip_from && j < skip_to) continue;
+        const bool is_q = head < Hq;
+        const int first = (is_q ? head : head - Hq) * D;
+        const __nv_bfloat16* src = (is_q ? q : k) + first;
+        const TW* w = is_q ? wq : wk;
+        const float inv = is_q ? inv_q : inv_k;
+        __nv_bfloat16* dst = is_q ? q + first : (k_dst ? k_dst + first : nullptr);
+        if (!dst) continue;
+        float a[8], wa[8];
+        unpack8(*reinterpret_cast<const Bf16x8*>(src + j * 8), a);
+        load_weights8(w, first + j * 8, inv, wa);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[e] *= wa[e];
+        if (j >= rot_groups) {  // behind the rotated columns
+            *reinterpret_cast<Bf16x8*>(dst + j * 8) = pack8(a);
+        } else if (interleaved) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float rx, ry;
+                rotate(a[2 * e], a[2 * e + 1], cs[j * 4 + e], sn[j * 4 + e], rx, ry);
+                a[2 * e] = pos_ok ? rx : 0.0f;
+                a[2 * e + 1] = pos_ok ? ry : 0.0f;
+            }
+            *reinterpret_cast<Bf16x8*>(dst + j * 8) = pack8(a);
+        } else {
+            float b[8], wb[8];
+            unpack8(*reinterpret_cast<const Bf16x8*>(src + rot_half + j * 8), b);
+            load_weights8(w, first + rot_half + j * 8, inv, wb);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                float rx, ry;
+                rotate(a[e], b[e] * wb[e], cs[j * 8 + e], sn[j * 8 + e], rx, ry);
+                a[e] = pos_ok ? rx : 0.0f;
+                b[e] = pos_ok ? ry : 0.0f;
+            }
+            *reinterpret_cast<Bf16x8*>(dst + j * 8) = pack8(a);
+            *reinterpret_cast<Bf16x8*>(dst + rot_half + j * 8) = pack8(b);
+        }
+    }
+    if (v_dst)
+        for (int i = threadIdx.x; i < Hkv * DV / 8; i += blockDim.x)
+            *reinterpret_cast<Bf16x8*>(v_dst + i * 8) = *reinterpret_cast<const Bf16x8*>(v + i * 8);
+}
+
 // wq/wk null: no norm.  cos/sin null (rot_half 0): no rotation.  k_cache null: q only.
 KB_EXPORT int kb_projection_norm_rope_write(void* packed, int stride, int is_bf16, int T, int k_offset, int v_offset, int Hq, int Hkv,
                                             int D, int DV, const void* wq, const void* wk, int w_bf16, float eps,
@@ -122,11 +261,23 @@ KB_EXPORT int kb_projection_norm_rope_write(void* packed, int stride, int is_bf1
     kb_launch(projection_norm_rope_write_kernel<TT, TW>, dim3(T), dim3(PR_THREADS), 0, stream, (TT*)packed, stride, k_offset,         \
               v_offset, Hq, Hkv, D, DV, (const TW*)wq, (const TW*)wk, eps, cos_table, sin_table, rot_half, max_pos, interleaved,     \
               positions, row_ids, block_table, max_pages, write_from, (TT*)k_cache, (TT*)v_cache, page_size, num_pages, num_rows, flag)
-    if (is_bf16) {
+    // whole 16-byte groups everywhere: heads, offsets, rows, the rotated part (split halves: each half) and the pages
+    const bool groups_of_eight = is_bf16 && D % 8 == 0 && DV % 8 == 0 && stride % 8 == 0 && k_offset % 8 == 0 && v_offset % 8 == 0 &&
+                                 (interleaved ? rot_half % 4 == 0 : rot_half % 8 == 0) && (uintptr_t)packed % 16 == 0 &&
+                                 (uintptr_t)k_cache % 16 == 0 && (uintptr_t)v_cache % 16 == 0;
+#define LAUNCH_VEC(TW)                                                                                                              \
+    kb_launch(projection_norm_rope_write_vec_kernel<TW>, dim3(T), dim3(PR_THREADS), 0, stream, (__nv_bfloat16*)packed, stride,        \
+              k_offset, v_offset, Hq, Hkv, D, DV, (const TW*)wq, (const TW*)wk, eps, cos_table, sin_table, rot_half, max_pos,        \
+              interleaved, positions, row_ids, block_table, max_pages, write_from, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, \
+              page_size, num_pages, num_rows, flag)
+    if (groups_of_eight) {
+        if (w_bf16) LAUNCH_VEC(__nv_bfloat16); else LAUNCH_VEC(float);
+    } else if (is_bf16) {
         if (w_bf16) LAUNCH(__nv_bfloat16, __nv_bfloat16); else LAUNCH(__nv_bfloat16, float);
     } else {
         if (w_bf16) LAUNCH(float, __nv_bfloat16); else LAUNCH(float, float);
     }
 #undef LAUNCH
+#undef LAUNCH_VEC
     return kb_launch_result();
 }

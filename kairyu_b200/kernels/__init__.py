@@ -598,7 +598,7 @@ def diff_attention_mma(
         launch(ctx.decode_rows, ctx.decode_tokens, ctx.num_decode_rows, 1)
 
 
-ATTENTION_MMA_SINKS = True  # the tensor-core attention kernels take sink logits (the mma.sync pair does; with sinks the TMA-fed kernels are passed by)
+ATTENTION_MMA_SINKS = True  # the tensor-core attention kernels take sink logits, in the step that divides a row's result
 
 DECODE_SPLIT = 128  # keys per split of the split-KV kernel (csrc/attention_mma.cu: DEC_SPLIT)
 
@@ -686,7 +686,8 @@ def attention_prefill_mma(
     when its grid makes two waves or more; ``two_tiles`` overrides that choice (tests).
 
     ``sinks``: fp32 [heads], a logit a head whose exp joins the softmax's denominator.  ``gate``: bf16 [tokens, >= heads *
-    head_dim], columns laid out as ``out``'s; the result is multiplied by its sigmoid.  The mma.sync kernel takes both."""
+    head_dim], columns laid out as ``out``'s; the result is multiplied by its sigmoid.  Every kernel here takes both, in its
+    last step (the tcgen05 kernels a gate whose rows are whole 16-byte groups)."""
     what = "attention_prefill_mma"
     _need_cuda(what, q, out, k_cache, v_cache, qo_indptr, seq_lens, block_table, tile_rows, tile_starts, sinks, gate)
     _check_sinks(what, num_q_heads, sinks)
@@ -696,11 +697,12 @@ def attention_prefill_mma(
     num_pages, page_size, num_kv_heads, head_dim = k_cache.shape
     if not attention_mma_supported(head_dim, num_q_heads, num_kv_heads):
         raise KernelError(f"{what}: head_dim {head_dim} with {num_q_heads}/{num_kv_heads} heads is not supported")
-    if sinks is None and gate is None and _prefill_tc5_ok(q, out, k_cache, v_cache):  # tcgen05 + TMA: S and O in tensor memory
+    gate_by_16 = gate is None or (gate.stride(0) % 8 == 0 and gate.data_ptr() % 16 == 0)  # the tcgen05 kernel reads it in 16-byte groups
+    if gate_by_16 and _prefill_tc5_ok(q, out, k_cache, v_cache):  # tcgen05 + TMA: S and O in tensor memory
         fn = _fn(
             "attention_prefill_tc5",
             "kb_attention_prefill_tc5",
-            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
         )
         merged = bool(_fn("attention_prefill_tc5", "kb_attention_prefill_tc5_merged", [c_int, c_int])(head_dim, page_size))
         splits = 1
@@ -732,7 +734,8 @@ def attention_prefill_mma(
                 tile_rows.data_ptr(), tile_starts.data_ptr(), int(num_tiles), num_q_heads, num_kv_heads, head_dim,
                 page_size, num_pages, float(scale), int(window), splits, _ptr(part_o), _ptr(part_ml),
                 wide_tiles[1].data_ptr() if use_two else None, wide_tiles[2].data_ptr() if use_two else None,
-                int(wide_tiles[0]) if use_two else 0, 1 if use_two else 0, _ptr(flag), _stream(),
+                int(wide_tiles[0]) if use_two else 0, 1 if use_two else 0, _ptr(sinks), _ptr(gate), gate.stride(0) if gate is not None else 0,
+                _ptr(flag), _stream(),
             ),
             what,
             launches=2 if splits > 1 else 1,
@@ -777,8 +780,9 @@ def attention_decode_mma(
 ) -> None:
     """Split-KV attention of rows that carry one token (bf16), then the merge.
 
-    ``sinks``: fp32 [heads], a logit a head whose exp joins the softmax's denominator in the merge.  ``gate``: bf16 [tokens, >=
-    heads * head_dim]; the merge multiplies the result by its sigmoid.  The mma.sync kernel takes both.
+    ``sinks``: fp32 [heads], a logit a head whose exp joins the softmax's denominator.  ``gate``: bf16 [tokens, >= heads *
+    head_dim]; the result is multiplied by its sigmoid.  Both act where a row's result is divided (the merge, or the TMA-fed
+    kernel itself when it runs one split).
 
     ``max_seq_len`` bounds every row's length; it sizes the grid and the scratch
     (``workspace.flat`` gives persistent fp32 buffers).  ``num_splits`` overrides the
@@ -793,7 +797,7 @@ def attention_decode_mma(
     num_pages, page_size, num_kv_heads, head_dim = k_cache.shape
     if not attention_mma_supported(head_dim, num_q_heads, num_kv_heads):
         raise KernelError(f"{what}: head_dim {head_dim} with {num_q_heads}/{num_kv_heads} heads is not supported")
-    if sinks is None and gate is None and _decode_tma_ok(k_cache, v_cache):  # tiled TMA copies of whole runs of key rows, streamed through a ring
+    if _decode_tma_ok(k_cache, v_cache):  # tiled TMA copies of whole runs of key rows, streamed through a ring
         splits_fn = _fn("attention_decode_tma", "kb_attention_decode_tma_splits", [c_int, c_int, c_int, c_int])
         if num_splits is None:
             num_splits = splits_fn(int(num_rows), num_kv_heads, head_dim, max(1, int(max_seq_len)))
@@ -804,7 +808,7 @@ def attention_decode_mma(
         fn = _fn(
             "attention_decode_tma",
             "kb_attention_decode_tma",
-            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
         )
         joined = _joined_cache_map(k_cache, v_cache)  # keys and values in one copy where the cache allows
         map_k = joined or _cache_map(k_cache, bands=True)
@@ -814,7 +818,8 @@ def attention_decode_mma(
                 map_k, map_v, q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0),
                 seq_lens.data_ptr(), block_table.data_ptr(), block_table.shape[1], decode_rows.data_ptr(),
                 decode_tokens.data_ptr(), int(num_rows), num_q_heads, num_kv_heads, head_dim, page_size, num_pages,
-                float(scale), int(window), num_splits, part_o.data_ptr(), part_ml.data_ptr(), 1 if joined else 0, _ptr(flag), _stream(),
+                float(scale), int(window), num_splits, part_o.data_ptr(), part_ml.data_ptr(), 1 if joined else 0, _ptr(sinks), _ptr(gate),
+                gate.stride(0) if gate is not None else 0, _ptr(flag), _stream(),
             ),
             what,
             launches=_fn("attention_decode_tma", "kb_attention_decode_tma_launches", [c_int])(num_splits),

@@ -71,7 +71,7 @@ CASES: dict[str, tuple[dict, int, int]] = {
     ], loop=(0, 1, 3), eps=1e-6), 42, 16),
     # no loop; the widest rows; one expert of one; four query heads a key/value head; the whole head rotated
     "wide": (config(64, 131, [
-        layer(latent(5, 32, 64, 48, 128, 0.12, base=250000.0), moe(1, 1, 32)),
+        layer(latent(5, 32, 64, 48, 128, 0.12, base=40000.0), moe(1, 1, 32)),
         layer(gated(4, 1, 128, 64, 0.09, 128), moe(5, 1, 24, shared=40)),
         layer(gated(2, 2, 64, 128, 0.12, 32), dense(96, 3.0)),
     ]), 43, 16),

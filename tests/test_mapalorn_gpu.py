@@ -104,7 +104,7 @@ def test_every_cut_matches_plain(case, dtype, decode_mode):
 
 MIXERS = {
     "latent narrow": latent(2, 16, 16, 16, 16, 0.3),                 # rows of 32: tensor cores in bfloat16
-    "latent rows of 128": latent(6, 32, 32, 24, 96, 0.2, base=250000.0),
+    "latent rows of 128": latent(5, 32, 48, 24, 80, 0.2, base=5000.0),
     "latent rows of 256": latent(3, 64, 64, 128, 192, 0.12),
     "latent many heads": latent(20, 16, 8, 16, 40, 0.3),             # more heads than one attention call takes
     "latent odd": latent(3, 10, 6, 14, 26, 0.4, base=77.0),          # rows that are no multiple of 16: 32-bit arithmetic in both modes
@@ -143,15 +143,18 @@ def _attention_reference(q, k, v, scale, sinks, positions):
     return torch.einsum("hij,jhd->ihd", p, vv).reshape(q.shape[0], heads * v.shape[2])[positions]
 
 
-@pytest.mark.parametrize("variant", ["float32 generic", "bfloat16 generic", "bfloat16 tensor cores"])
-@pytest.mark.parametrize("sizes", [(4, 2, 32, 16), (16, 1, 128, 64), (3, 3, 64, 128)])
+@pytest.mark.parametrize("variant", ["float32 generic", "bfloat16 generic", "bfloat16 tensor cores", "bfloat16 tensor cores, keys split",
+                                     "bfloat16 tensor cores, two tiles a block"])
+@pytest.mark.parametrize("sizes", [(4, 2, 32, 16), (16, 1, 128, 64), (3, 3, 64, 128), (8, 2, 128, 16)])
 def test_keys_and_sinks_that_stand_out(variant, sizes):
     """The attention kernels alone over a 900-token sequence in shuffled pages.  Among keys whose scores are near
     zero, one key a query is given a score of 18: at distances 0 and 1, at a page's last and first place, at the
     sequence's first tokens and hundreds of tokens away; leaving it out moves the result by half its size.  The sinks
     are as large as those scores (some heads) or far below (others), so that a sink that is left out, scaled or counted
     twice changes every weight.  With a gate.  The same queries run as one prompt, as a portion that starts in the middle
-    of a page beside single tokens of other lengths, and as single tokens alone."""
+    of a page beside single tokens of other lengths, and as single tokens alone.  Heads of 64 and 128 take the tcgen05
+    kernels for prompt portions: one query tile a block, a tile's keys split over three blocks whose parts a second kernel
+    joins, and two query tiles a block; the other sizes and single tokens the mma.sync kernels."""
     from kairyu_b200 import kernels
     from kairyu_b200.engine.workspace import Workspace
 
@@ -208,10 +211,21 @@ def test_keys_and_sinks_that_stand_out(variant, sizes):
         single = [r for r in range(rows) if counts[r] == 1]
         common = dict(seq_lens=torch.tensor(seq_lens, **i32), block_table=table, num_q_heads=H, scale=scale, sinks=sinks_gpu, gate=gate_rows)
         if tile_rows:
+            extra = {}
+            if variant.endswith("keys split"):
+                extra = dict(workspace=Workspace("cuda"), num_splits=3, max_seq_len=max(seq_lens))
+            wide = kernels.attention_prefill_wide_tile_rows(D)
+            if variant.endswith("two tiles a block") and wide:
+                wide_rows = [r for r in range(rows) if counts[r] > 1 for _ in range(0, counts[r], wide)]
+                wide_starts = [s for r in range(rows) if counts[r] > 1 for s in range(0, counts[r], wide)]
+                extra = dict(wide_tiles=(len(wide_rows), torch.tensor(wide_rows, **i32), torch.tensor(wide_starts, **i32)), two_tiles=True,
+                             max_seq_len=max(seq_lens))
             kernels.attention_prefill_mma(q_rows, out, k_cache, v_cache, qo_indptr=torch.tensor(qo_indptr, **i32), tile_rows=torch.tensor(tile_rows, **i32),
-                                          tile_starts=torch.tensor(tile_starts, **i32), num_tiles=len(tile_rows), **common)
+                                          tile_starts=torch.tensor(tile_starts, **i32), num_tiles=len(tile_rows), **extra, **common)
         if single:
-            kernels.attention_decode_mma(q_rows, out, k_cache, v_cache, decode_rows=torch.tensor(single, **i32),
+            # the TMA-fed kernel (heads of 64 and up): as many splits as it chooses, three (a merge kernel divides), or one (it divides itself)
+            splits = 3 if variant.endswith("keys split") else 1 if variant.endswith("two tiles a block") else None
+            kernels.attention_decode_mma(q_rows, out, k_cache, v_cache, decode_rows=torch.tensor(single, **i32), num_splits=splits,
                                          decode_tokens=torch.tensor([qo_indptr[r] for r in single], **i32), num_rows=len(single),
                                          max_seq_len=max(seq_lens), workspace=Workspace("cuda"), **common)
         return out
@@ -295,6 +309,37 @@ def test_feed_forwards_alone(sizes, dtype):
     assert (other - want).abs().max() > 5 * bound * want.abs().max()
 
 
+def _projection_case(kernels, plain, g, dtype, tokens, page, heads, kvh, dim, vdim, rot, spare, block_table, row_ids, where, write_from):
+    k_off, v_off = heads * dim, heads * dim + kvh * dim
+    angles = plain.angles(torch.arange(64), rot, 100.0)
+    cos, sin = angles.cos().float().cuda(), angles.sin().float().cuda()
+    qw = (1 + 0.2 * torch.randn(heads * dim, generator=g)).to(torch.bfloat16)
+    kw = (1 + 0.2 * torch.randn(kvh * dim, generator=g)).to(torch.bfloat16)
+    for interleaved, turn in ((False, plain.rotate_halves), (True, plain.rotate_interleaved)):
+        source = torch.randn(tokens, v_off + kvh * vdim + spare, generator=g).to(dtype)
+        packed = source.clone().cuda()
+        k_cache = torch.zeros(9, page, kvh, dim, dtype=dtype, device="cuda")
+        v_cache = torch.zeros(9, page, kvh, vdim, dtype=dtype, device="cuda")
+        kernels.projection_norm_rope_write(
+            packed, num_q_heads=heads, num_kv_heads=kvh, head_dim=dim, value_dim=vdim, k_offset=k_off, v_offset=v_off, positions=where, row_ids=row_ids,
+            q_norm_weight=qw.to(dtype).cuda(), k_norm_weight=kw.to(dtype).cuda(), eps=1e-5, cos=cos, sin=sin, interleaved=interleaved,
+            block_table=block_table, write_from=write_from, k_cache=k_cache, v_cache=v_cache)
+        s = source.double()
+        q_want = turn(plain.rms_norm(s[:, :k_off], qw.double(), 1e-5).view(tokens, heads, dim), where.cpu(), rot, 100.0).reshape(tokens, -1)
+        k_want = turn(plain.rms_norm(s[:, k_off:v_off], kw.double(), 1e-5).view(tokens, kvh, dim), where.cpu(), rot, 100.0).reshape(tokens, -1)
+        tolerance = 1e-5 if dtype == torch.float32 else 0.03
+        assert (packed[:, :k_off].cpu().double() - q_want).abs().max() < tolerance
+        assert torch.equal(packed[:, v_off:].cpu(), source[:, v_off:])
+        for t in range(tokens):
+            position, row = int(where[t]), int(row_ids[t])
+            slot = (int(block_table[row, position // page]), position % page)
+            if position >= int(write_from[row]):
+                assert (k_cache[slot].flatten().cpu().double() - k_want[t]).abs().max() < tolerance
+                assert torch.equal(v_cache[slot].flatten().cpu(), source[t, v_off : v_off + kvh * vdim])
+            else:
+                assert not k_cache[slot].any() and not v_cache[slot].any()
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_small_kernels(dtype):
     """The layer norm with two pending sums and on listed rows, the norm over a whole projection with both rotary layouts
@@ -320,39 +365,15 @@ def test_small_kernels(dtype):
     kernels.layernorm(residual, weight.to(dtype).cuda(), bias.to(dtype).cuda(), 1e-5, few, rows=rows)
     assert torch.equal(few, out[rows.long()])
 
-    page, heads, kvh, dim, vdim, rot = 8, 3, 1, 20, 12, 8
-    k_off, v_off = heads * dim, heads * dim + kvh * dim
+    page = 8
     block_table = torch.tensor([[3, 1, 7, 5, 2, -1], [4, 6, 8, -1, -1, -1]], dtype=torch.int32, device="cuda")
     row_ids = torch.tensor([0] * 30 + [1] * 7, dtype=torch.int32, device="cuda")
     where = torch.tensor(list(range(5, 35)) + list(range(11, 18)), dtype=torch.int32, device="cuda")
     write_from = torch.tensor([8, 0], dtype=torch.int32, device="cuda")  # row 0 only reads its first page
-    angles = plain.angles(torch.arange(64), rot, 100.0)
-    cos, sin = angles.cos().float().cuda(), angles.sin().float().cuda()
-    qw = (1 + 0.2 * torch.randn(heads * dim, generator=g)).to(torch.bfloat16)
-    kw = (1 + 0.2 * torch.randn(kvh * dim, generator=g)).to(torch.bfloat16)
-    for interleaved, turn in ((False, plain.rotate_halves), (True, plain.rotate_interleaved)):
-        source = torch.randn(tokens, v_off + kvh * vdim + 5, generator=g).to(dtype)
-        packed = source.clone().cuda()
-        k_cache = torch.zeros(9, page, kvh, dim, dtype=dtype, device="cuda")
-        v_cache = torch.zeros(9, page, kvh, vdim, dtype=dtype, device="cuda")
-        kernels.projection_norm_rope_write(
-            packed, num_q_heads=heads, num_kv_heads=kvh, head_dim=dim, value_dim=vdim, k_offset=k_off, v_offset=v_off, positions=where, row_ids=row_ids,
-            q_norm_weight=qw.to(dtype).cuda(), k_norm_weight=kw.to(dtype).cuda(), eps=1e-5, cos=cos, sin=sin, interleaved=interleaved,
-            block_table=block_table, write_from=write_from, k_cache=k_cache, v_cache=v_cache)
-        s = source.double()
-        q_want = turn(plain.rms_norm(s[:, :k_off], qw.double(), 1e-5).view(tokens, heads, dim), where.cpu(), rot, 100.0).reshape(tokens, -1)
-        k_want = turn(plain.rms_norm(s[:, k_off:v_off], kw.double(), 1e-5).view(tokens, kvh, dim), where.cpu(), rot, 100.0).reshape(tokens, -1)
-        tolerance = 1e-5 if dtype == torch.float32 else 0.03
-        assert (packed[:, :k_off].cpu().double() - q_want).abs().max() < tolerance
-        assert torch.equal(packed[:, v_off:].cpu(), source[:, v_off:])
-        for t in range(tokens):
-            position, row = int(where[t]), int(row_ids[t])
-            slot = (int(block_table[row, position // page]), position % page)
-            if position >= int(write_from[row]):
-                assert (k_cache[slot].flatten().cpu().double() - k_want[t]).abs().max() < tolerance
-                assert torch.equal(v_cache[slot].flatten().cpu(), source[t, v_off : v_off + kvh * vdim])
-            else:
-                assert not k_cache[slot].any() and not v_cache[slot].any()
+    # widths that are no whole 16 bytes (an element a thread), and rows of whole 16-byte groups (eight a thread in bfloat16):
+    # part of a head rotated, and all of it
+    for heads, kvh, dim, vdim, rot, spare in ((3, 1, 20, 12, 8, 5), (3, 2, 32, 16, 16, 8), (2, 1, 64, 24, 64, 0), (4, 4, 16, 8, 8, 16)):
+        _projection_case(kernels, plain, g, dtype, tokens, page, heads, kvh, dim, vdim, rot, spare, block_table, row_ids, where, write_from)
 
     # the latent row: [heads * (dim + rot) query | rank latent | rot key part]
     heads, dim, rot, rank = 3, 10, 6, 18
