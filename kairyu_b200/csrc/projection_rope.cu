@@ -112,10 +112,23 @@ struct alignas(16) Bf16x8 {
     __nv_bfloat162 v[4];
 };
 
-template <typename TW>
-__device__ __forceinline__ void load_weights8(const TW* w, int at, float inv, float (&out)[8]) {
+__device__ __forceinline__ void unpack8(const Bf16x8& in, float (&out)[8]);
+
+// eight weights from a 16-byte aligned place (at is a multiple of 8), times inv: one or two 16-byte loads
+__device__ __forceinline__ void load_weights8(const __nv_bfloat16* w, int at, float inv, float (&out)[8]) {
+    if (w) unpack8(*reinterpret_cast<const Bf16x8*>(w + at), out);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) out[e] = w ? inv * to_float(w[at + e]) : inv;
+    for (int e = 0; e < 8; ++e) out[e] = w ? inv * out[e] : inv;
+}
+
+__device__ __forceinline__ void load_floats(const float* at, int count, float* out) {  // count 4 or 8, 16-byte aligned
+    for (int e = 0; e < count; e += 4) *reinterpret_cast<float4*>(out + e) = *reinterpret_cast<const float4*>(at + e);
+}
+
+__device__ __forceinline__ void load_weights8(const float* w, int at, float inv, float (&out)[8]) {
+    if (w) load_floats(w + at, 8, out);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) out[e] = w ? inv * out[e] : inv;
 }
 
 __device__ __forceinline__ void unpack8(const Bf16x8& in, float (&out)[8]) {
@@ -216,10 +229,13 @@ projection_norm_rope_write_vec_kernel(__nv_bfloat16* __restrict__ packed, int st
         if (j >= rot_groups) {  // behind the rotated columns
             *reinterpret_cast<Bf16x8*>(dst + j * 8) = pack8(a);
         } else if (interleaved) {
+            float c4[4], s4[4];
+            load_floats(cs + j * 4, 4, c4);
+            load_floats(sn + j * 4, 4, s4);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 float rx, ry;
-                rotate(a[2 * e], a[2 * e + 1], cs[j * 4 + e], sn[j * 4 + e], rx, ry);
+                rotate(a[2 * e], a[2 * e + 1], c4[e], s4[e], rx, ry);
                 a[2 * e] = pos_ok ? rx : 0.0f;
                 a[2 * e + 1] = pos_ok ? ry : 0.0f;
             }
@@ -228,10 +244,13 @@ projection_norm_rope_write_vec_kernel(__nv_bfloat16* __restrict__ packed, int st
             float b[8], wb[8];
             unpack8(*reinterpret_cast<const Bf16x8*>(src + rot_half + j * 8), b);
             load_weights8(w, first + rot_half + j * 8, inv, wb);
+            float c8[8], s8[8];
+            load_floats(cs + j * 8, 8, c8);
+            load_floats(sn + j * 8, 8, s8);
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 float rx, ry;
-                rotate(a[e], b[e] * wb[e], cs[j * 8 + e], sn[j * 8 + e], rx, ry);
+                rotate(a[e], b[e] * wb[e], c8[e], s8[e], rx, ry);
                 a[e] = pos_ok ? rx : 0.0f;
                 b[e] = pos_ok ? ry : 0.0f;
             }
@@ -264,7 +283,8 @@ KB_EXPORT int kb_projection_norm_rope_write(void* packed, int stride, int is_bf1
     // whole 16-byte groups everywhere: heads, offsets, rows, the rotated part (split halves: each half) and the pages
     const bool groups_of_eight = is_bf16 && D % 8 == 0 && DV % 8 == 0 && stride % 8 == 0 && k_offset % 8 == 0 && v_offset % 8 == 0 &&
                                  (interleaved ? rot_half % 4 == 0 : rot_half % 8 == 0) && (uintptr_t)packed % 16 == 0 &&
-                                 (uintptr_t)k_cache % 16 == 0 && (uintptr_t)v_cache % 16 == 0;
+                                 (uintptr_t)k_cache % 16 == 0 && (uintptr_t)v_cache % 16 == 0 && (uintptr_t)wq % 16 == 0 &&
+                                 (uintptr_t)wk % 16 == 0 && (uintptr_t)cos_table % 16 == 0 && (uintptr_t)sin_table % 16 == 0;
 #define LAUNCH_VEC(TW)                                                                                                              \
     kb_launch(projection_norm_rope_write_vec_kernel<TW>, dim3(T), dim3(PR_THREADS), 0, stream, (__nv_bfloat16*)packed, stride,        \
               k_offset, v_offset, Hq, Hkv, D, DV, (const TW*)wq, (const TW*)wk, eps, cos_table, sin_table, rot_half, max_pos,        \

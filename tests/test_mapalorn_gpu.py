@@ -109,8 +109,14 @@ MIXERS = {
     "latent many heads": latent(20, 16, 8, 16, 40, 0.3),             # more heads than one attention call takes
     "latent odd": latent(3, 10, 6, 14, 26, 0.4, base=77.0),          # rows that are no multiple of 16: 32-bit arithmetic in both modes
     "latent one head": latent(1, 24, 2, 8, 30, 0.3),
+    "latent rows of 64": latent(4, 16, 16, 16, 48, 0.3),             # the tcgen05 and TMA-fed kernels over rows that are keys and values at once
+    "latent rows of 192": latent(2, 32, 32, 32, 160, 0.2, base=3000.0),
+    "latent rows of 96": latent(3, 48, 32, 16, 64, 0.2),             # padded to 128 in shared memory
     "gated equal widths": gated(4, 2, 32, 32, 0.25, 16),             # tensor cores in bfloat16
     "gated heads of 128": gated(2, 1, 128, 128, 0.1, 128),
+    "gated heads of 64": gated(4, 1, 64, 64, 0.2, 32, base=2000.0),
+    "gated heads of 96": gated(6, 3, 96, 96, 0.15, 48),
+    "gated heads of 256": gated(2, 2, 256, 256, 0.08, 64),
     "gated sixteen a group": gated(16, 1, 16, 16, 0.3, 8, base=300.0),
     "gated wider values": gated(3, 3, 16, 40, 0.4, 16),              # 32-bit arithmetic in both modes
     "gated narrower values": gated(6, 2, 48, 16, 0.2, 24),
