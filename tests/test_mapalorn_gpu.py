@@ -151,7 +151,7 @@ def _attention_reference(q, k, v, scale, sinks, positions):
 
 @pytest.mark.parametrize("variant", ["float32 generic", "bfloat16 generic", "bfloat16 tensor cores", "bfloat16 tensor cores, keys split",
                                      "bfloat16 tensor cores, two tiles a block"])
-@pytest.mark.parametrize("sizes", [(4, 2, 32, 16), (16, 1, 128, 64), (3, 3, 64, 128), (8, 2, 128, 16)])
+@pytest.mark.parametrize("sizes", [(4, 2, 32, 16), (16, 1, 128, 64), (3, 3, 64, 128), (8, 2, 128, 16), (2, 1, 256, 16), (4, 1, 192, 32), (6, 2, 96, 8)])
 def test_keys_and_sinks_that_stand_out(variant, sizes):
     """The attention kernels alone over a 900-token sequence in shuffled pages.  Among keys whose scores are near
     zero, one key a query is given a score of 18: at distances 0 and 1, at a page's last and first place, at the
