@@ -21,7 +21,7 @@ class ConfigError(ValueError):
 class RopeScaling:
     """Frequency scaling of the rotary table (kairyu/models/config.py:58-72)."""
 
-    kind: str  # "llama3" | "yarn"
+    kind: str  # "llama3" | "yarn" | "linear" (every frequency divided by ``factor``)
     factor: float
     low_freq_factor: float = 1.0
     high_freq_factor: float = 4.0

@@ -28,26 +28,16 @@
 // Every sum runs in an order that depends on the sizes alone, never on the batch or on how a
 // prompt was cut: tokens are staged in chunks of sixteen, but a chunk's edge changes no arithmetic.
 #include "common.cuh"
+#include "linear_recurrence.cuh"
 
-#define DELTA_MAX_TAPS 16
-#define DELTA_CHUNK 16
-#define DELTA_WARPS 8
-
-__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
-
-// input of the convolution `back` tokens before token t (offset o within its row's portion)
-template <typename TA>
-__device__ __forceinline__ float conv_input(const TA* __restrict__ proj, int stride, const float* __restrict__ kept,
-                                            int C, int n, int t, int o, int back, int c) {
-    if (o - back >= 0) return to_float(proj[(size_t)(t - back) * stride + c]);
-    return kept[(size_t)((n - 1) + (o - back)) * C + c];
-}
+#define DELTA_MAX_TAPS LR_MAX_TAPS
 
 // NT: the number of taps where it is one of the usual few (the taps' loop unrolls, the rows of the last
 // tokens are looked up once a token, a channel's taps come in one load); 0: any number, taken at run time.
 template <typename TA, int NT>
 __global__ void __launch_bounds__(128)
-delta_prepare_kernel(const TA* __restrict__ proj, int stride, const float* __restrict__ gates, const float* __restrict__ taps,
+delta_prepare_kernel(const TA* __restrict__ proj, int stride, const float* __restrict__ gates, int gate_stride,
+                     const float* __restrict__ channel_a, const float* __restrict__ taps,
                      int n, const float* __restrict__ conv_state, const int* __restrict__ row_ids,
                      const int* __restrict__ qo_indptr, const int* __restrict__ state_slots,
                      const float* __restrict__ A_log, const float* __restrict__ dt_bias, int KH, int D, int H, int V,
@@ -126,178 +116,28 @@ delta_prepare_kernel(const TA* __restrict__ proj, int stride, const float* __res
         const int first = (unit - 2 * KH) * V;
         for (int e = lane; e < V; e += 32) vv[(size_t)t * H * V + first + e] = silu_f(convolve(2 * KH * D + first + e));
     }
+    if (channel_a) {
+        // one decay a head and key channel: a comes as [tokens, H * D], dt_bias has H * D entries; beta alone in `gates`
+        for (int h = threadIdx.x; blockIdx.y == 0 && h < H; h += blockDim.x)
+            beta[(size_t)t * H + h] = 1.0f / (1.0f + expf(-gates[(size_t)t * gate_stride + h]));
+        for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H * D; i += gridDim.y * blockDim.x) {
+            const float a = channel_a[(size_t)t * H * D + i] + dt_bias[i];
+            decay[(size_t)t * H * D + i] = expf(-expf(A_log[i / D]) * softplus_f(a));
+        }
+        return;
+    }
     for (int h = threadIdx.x; blockIdx.y == 0 && h < H; h += blockDim.x) {
-        const float b = gates[(size_t)t * 2 * H + h];
-        const float a = gates[(size_t)t * 2 * H + H + h] + dt_bias[h];
-        const float softplus = a > 20.0f ? a : log1pf(expf(a));
+        const float b = gates[(size_t)t * gate_stride + h];
+        const float a = gates[(size_t)t * gate_stride + H + h] + dt_bias[h];
         beta[(size_t)t * H + h] = 1.0f / (1.0f + expf(-b));
-        decay[(size_t)t * H + h] = expf(-expf(A_log[h]) * softplus);
+        decay[(size_t)t * H + h] = expf(-expf(A_log[h]) * softplus_f(a));
     }
 }
 
+// gate: [tokens, H * V] columns of a row of `gate_stride` entries; sigmoid_gate: sigmoid(gate), else silu(gate)
 template <typename TA>
 __global__ void __launch_bounds__(128)
-delta_conv_state_kernel(const TA* __restrict__ proj, int stride, float* __restrict__ conv_state, int n, int C,
-                        const int* __restrict__ qo_indptr, const int* __restrict__ state_slots) {
-    const int row = blockIdx.x;
-    const int c = blockIdx.y * blockDim.x + threadIdx.x;
-    const int t0 = qo_indptr[row];
-    const int count = qo_indptr[row + 1] - t0;
-    float* kept = conv_state + (size_t)state_slots[row] * (n - 1) * C;
-    pdl_wait();
-    if (c >= C || count < 1) return;
-    float next[DELTA_MAX_TAPS];
-#pragma unroll
-    for (int i = 0; i < DELTA_MAX_TAPS; ++i) {
-        if (i < n - 1) {
-            const int off = count - (n - 1) + i;
-            next[i] = off >= 0 ? to_float(proj[(size_t)(t0 + off) * stride + c]) : kept[(size_t)((n - 1) + off) * C + c];
-        }
-    }
-#pragma unroll
-    for (int i = 0; i < DELTA_MAX_TAPS; ++i)
-        if (i < n - 1) kept[(size_t)i * C + c] = next[i];
-}
-
-template <int DPT, int LANES, bool PREFETCH>
-__global__ void __launch_bounds__(32 * DELTA_WARPS)
-delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vv,
-                        const float* __restrict__ beta, const float* __restrict__ decay, float* __restrict__ states,
-                        const int* __restrict__ qo_indptr, const int* __restrict__ state_slots, int KH, int D, int H, int V,
-                        float* __restrict__ out) {
-    constexpr int LD = LANES * DPT;               // entries of a key or query row as staged (zeros beyond D)
-    constexpr int PER_WARP = 32 / LANES;          // columns of S a warp owns
-    constexpr int COLS = DELTA_WARPS * PER_WARP;  // columns a block owns
-    constexpr int CHUNK = LD <= 256 ? DELTA_CHUNK : DELTA_CHUNK / 2;  // tokens staged at a time (shared memory)
-    __shared__ __align__(16) float ks[CHUNK][LD];
-    __shared__ __align__(16) float qs[CHUNK][LD];
-    __shared__ float vs[CHUNK][COLS];
-    __shared__ float bs[CHUNK], gs[CHUNK], kqs[CHUNK];
-    const int row = blockIdx.x, h = blockIdx.y;
-    const int col0 = blockIdx.z * COLS;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int part = lane % LANES;                    // this lane holds entries part, part + LANES, ... of its column
-    const int local = warp * PER_WARP + lane / LANES;  // its column among the block's
-    const int col = col0 + local;
-    const int kh = h / (H / KH);
-    const int t0 = qo_indptr[row], t1 = qo_indptr[row + 1];
-    // the state is kept column by column ([heads, V, D]): a column is one run of memory
-    float* Sg = states + (((size_t)state_slots[row] * H + h) * V + (col < V ? col : 0)) * D;
-    pdl_wait();
-    float S[DPT];
-#pragma unroll
-    for (int m = 0; m < DPT; ++m) {
-        const int i = m * LANES + part;
-        S[m] = (i < D && col < V) ? Sg[i] : 0.0f;
-    }
-    // The next chunk's rows are fetched into registers while this chunk's tokens are walked, and put
-    // into shared memory behind the barrier that ends the walk: the loads' latency is off the chain.
-    constexpr int THREADS = 32 * DELTA_WARPS;
-    // (A step of single tokens has no next chunk, and runs leaner without: PREFETCH is off for it.)
-    constexpr int NP = PREFETCH ? CHUNK * LD / THREADS : 1;                    // key (and query) entries a thread fetches a chunk
-    constexpr int NV = PREFETCH ? (CHUNK * COLS + THREADS - 1) / THREADS : 1;  // value entries
-    float pk[NP], pq[NP], pv[NV], pb = 0.0f, pg = 0.0f;
-    auto fetch = [&](int c0) {
-        const int nt = min(CHUNK, t1 - c0);
-#pragma unroll
-        for (int j = 0; j < NP; ++j) {
-            const int idx = j * THREADS + threadIdx.x;
-            const int tt = idx / LD, i = idx % LD;
-            const bool live = tt < nt && i < D;
-            const size_t src = ((size_t)(c0 + tt) * KH + kh) * D + i;
-            pk[j] = live ? kn[src] : 0.0f;
-            pq[j] = live ? qn[src] : 0.0f;
-        }
-#pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            const int idx = j * THREADS + threadIdx.x;
-            const int tt = idx / COLS, c = idx % COLS;
-            pv[j] = (tt < nt && col0 + c < V) ? vv[((size_t)(c0 + tt) * H + h) * V + col0 + c] : 0.0f;
-        }
-        if (threadIdx.x < nt) {
-            pb = beta[(size_t)(c0 + threadIdx.x) * H + h];
-            pg = decay[(size_t)(c0 + threadIdx.x) * H + h];
-        }
-    };
-    if (PREFETCH && t0 < t1) fetch(t0);
-    for (int c0 = t0; c0 < t1; c0 += CHUNK) {
-        const int nt = min(CHUNK, t1 - c0);
-        __syncthreads();
-        if constexpr (PREFETCH) {
-#pragma unroll
-            for (int j = 0; j < NP; ++j) {
-                const int idx = j * THREADS + threadIdx.x;
-                ks[idx / LD][idx % LD] = pk[j];
-                qs[idx / LD][idx % LD] = pq[j];
-            }
-#pragma unroll
-            for (int j = 0; j < NV; ++j) {
-                const int idx = j * THREADS + threadIdx.x;
-                if (idx < CHUNK * COLS) vs[idx / COLS][idx % COLS] = pv[j];
-            }
-            if (threadIdx.x < CHUNK) {
-                bs[threadIdx.x] = pb;
-                gs[threadIdx.x] = pg;
-            }
-        } else {
-            for (int idx = threadIdx.x; idx < nt * LD; idx += blockDim.x) {
-                const int tt = idx / LD, i = idx % LD;
-                const size_t src = ((size_t)(c0 + tt) * KH + kh) * D + i;
-                ks[tt][i] = i < D ? kn[src] : 0.0f;
-                qs[tt][i] = i < D ? qn[src] : 0.0f;
-            }
-            for (int idx = threadIdx.x; idx < nt * COLS; idx += blockDim.x) {
-                const int tt = idx / COLS, j = idx % COLS;
-                vs[tt][j] = col0 + j < V ? vv[((size_t)(c0 + tt) * H + h) * V + col0 + j] : 0.0f;
-            }
-            if (threadIdx.x < nt) {
-                bs[threadIdx.x] = beta[(size_t)(c0 + threadIdx.x) * H + h];
-                gs[threadIdx.x] = decay[(size_t)(c0 + threadIdx.x) * H + h];
-            }
-        }
-        __syncthreads();
-        if (PREFETCH && c0 + CHUNK < t1) fetch(c0 + CHUNK);
-        for (int tt = warp; tt < nt; tt += DELTA_WARPS) {
-            float dot = 0.0f;
-            for (int i = lane; i < LD; i += 32) dot += ks[tt][i] * qs[tt][i];
-            dot = warp_sum(dot);
-            if (lane == 0) kqs[tt] = dot;
-        }
-        __syncthreads();
-        const bool upper = (part & (LANES / 2)) != 0;
-        for (int tt = 0; tt < nt; ++tt) {
-            float kv[DPT];
-            float a = 0.0f, b = 0.0f;
-#pragma unroll
-            for (int m = 0; m < DPT; ++m) {
-                kv[m] = ks[tt][m * LANES + part];
-                a = fmaf(S[m], kv[m], a);
-                b = fmaf(S[m], qs[tt][m * LANES + part], b);
-            }
-            // Both sums in one butterfly: the first exchange leaves the lower half of a column's lanes with the
-            // halves' sum of a and the upper half with that of b; the later stages add within each half.
-            const float given = __shfl_xor_sync(0xffffffffu, upper ? a : b, LANES / 2);
-            float z = (upper ? b : a) + given;
-#pragma unroll
-            for (int offset = LANES / 4; offset > 0; offset >>= 1) z += __shfl_xor_sync(0xffffffffu, z, offset);
-            a = __shfl_sync(0xffffffffu, z, lane & ~(LANES - 1));  // every lane needs a; b stays with the upper half
-            const float g = gs[tt];
-            const float u = bs[tt] * (vs[tt][local] - g * a);
-#pragma unroll
-            for (int m = 0; m < DPT; ++m) S[m] = fmaf(kv[m], u, g * S[m]);
-            if (part == LANES / 2 && col < V) out[((size_t)(c0 + tt) * H + h) * V + col] = g * z + kqs[tt] * u;
-        }
-    }
-#pragma unroll
-    for (int m = 0; m < DPT; ++m) {
-        const int i = m * LANES + part;
-        if (i < D && col < V) Sg[i] = S[m];
-    }
-}
-
-template <typename TA>
-__global__ void __launch_bounds__(128)
-delta_gated_norm_kernel(const float* __restrict__ o, const TA* __restrict__ proj, int stride, int gate_offset,
+delta_gated_norm_kernel(const float* __restrict__ o, const TA* __restrict__ gate, int gate_stride, int sigmoid_gate,
                         const float* __restrict__ w, float eps, int H, int V, TA* __restrict__ out) {
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
@@ -309,13 +149,16 @@ delta_gated_norm_kernel(const float* __restrict__ o, const TA* __restrict__ proj
         ss = warp_sum(ss);
         const float inv = rsqrtf(ss / (float)V + eps);
         for (int e = lane; e < V; e += 32) {
-            const float gate = to_float(proj[(size_t)t * stride + gate_offset + h * V + e]);
-            out[(size_t)t * H * V + h * V + e] = from_float<TA>(oh[e] * inv * w[e] * silu_f(gate));
+            const float z = to_float(gate[(size_t)t * gate_stride + h * V + e]);
+            const float factor = sigmoid_gate ? 1.0f / (1.0f + expf(-z)) : silu_f(z);
+            out[(size_t)t * H * V + h * V + e] = from_float<TA>(oh[e] * inv * w[e] * factor);
         }
     }
 }
 
-KB_EXPORT int kb_delta_prepare(const void* proj, int stride, int is_bf16, const float* gates, const float* taps, int n,
+// channel_a null: `gates` is [tokens, 2H] (beta's logits, then a) and the decay one number a head ([tokens, H]);
+// else `gates` is [tokens, H], channel_a [tokens, H * D], dt_bias [H * D] and the decay [tokens, H, D].
+KB_EXPORT int kb_delta_prepare(const void* proj, int stride, int is_bf16, const float* gates, const float* channel_a, const float* taps, int n,
                                float* conv_state, const int* row_ids, const int* qo_indptr, const int* state_slots,
                                const float* A_log, const float* dt_bias, int KH, int D, int H, int V, float* qn, float* kn,
                                float* vv, float* beta, float* decay, int num_rows, int T, int* flag, cudaStream_t stream) {
@@ -325,8 +168,9 @@ KB_EXPORT int kb_delta_prepare(const void* proj, int stride, int is_bf16, const 
     if (n < 1 || n > DELTA_MAX_TAPS + 1 || D < 1 || D > 512 || KH < 1 || H % KH != 0 || V < 1) return KB_ERR_UNSUPPORTED_SIZE;
     if (n > 1 && !conv_state) return KB_ERR_NULL;
     const int C = 2 * KH * D + H * V;
+    const int gate_stride = channel_a ? H : 2 * H;
 #define LAUNCH(TA, NT)                                                                                                        \
-    kb_launch(delta_prepare_kernel<TA, NT>, dim3(T, (2 * KH + H + 3) / 4), dim3(128), 0, stream, (const TA*)proj, stride, gates, taps, n,              \
+    kb_launch(delta_prepare_kernel<TA, NT>, dim3(T, (2 * KH + H + 3) / 4), dim3(128), 0, stream, (const TA*)proj, stride, gates, gate_stride, channel_a, taps, n, \
               (const float*)conv_state, row_ids, qo_indptr, state_slots, A_log, dt_bias, KH, D, H, V, qn, kn, vv, beta, decay, num_rows, flag)
 #define PICK(TA)                                                                                                              \
     do {                                                                                                                      \
@@ -338,46 +182,25 @@ KB_EXPORT int kb_delta_prepare(const void* proj, int stride, int is_bf16, const 
 #undef LAUNCH
     int code = kb_launch_result();
     if (code != 0 || n == 1) return code;
-    dim3 grid(num_rows, (C + 127) / 128);
-    if (is_bf16)
-        kb_launch(delta_conv_state_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)proj, stride, conv_state, n, C, qo_indptr, state_slots);
-    else
-        kb_launch(delta_conv_state_kernel<float>, grid, dim3(128), 0, stream, (const float*)proj, stride, conv_state, n, C, qo_indptr, state_slots);
-    return kb_launch_result();
+    return launch_conv_state(proj, stride, is_bf16, conv_state, n, C, qo_indptr, state_slots, num_rows, stream);
 }
 
+// channel_decay: decay is [tokens, H, D], else [tokens, H]
 KB_EXPORT int kb_delta_recurrence(const float* qn, const float* kn, const float* vv, const float* beta, const float* decay,
                                   float* states, const int* qo_indptr, const int* state_slots, int KH, int D, int H, int V,
-                                  float* out, int num_rows, int single_tokens, cudaStream_t stream) {
-    if (num_rows == 0) return 0;
-    if (!qn || !kn || !vv || !beta || !decay || !states || !qo_indptr || !state_slots || !out) return KB_ERR_NULL;
-    if (D < 1 || D > 512 || KH < 1 || H % KH != 0 || V < 1 || H > 65535) return KB_ERR_UNSUPPORTED_SIZE;
-    // Sixteen lanes a column whatever the step holds, so that a sum's order never depends on the batch
-    // (measured at dim 128, 16 heads, vdim 128: one row of 2,048 tokens 695 us against 742 at 32 lanes and 788
-    // at 8; four rows of 512 tokens 430 against 529 and 278; 64 rows of one token 31 against 41 at 32).
-    constexpr int LANES = 16;
-    const int cols = DELTA_WARPS * (32 / LANES);
-    dim3 grid(num_rows, H, (V + cols - 1) / cols);
-    const dim3 block(32 * DELTA_WARPS);
-#define LAUNCH(DPT, PF) kb_launch(delta_recurrence_kernel<DPT, LANES, PF>, grid, block, 0, stream, qn, kn, vv, beta, decay, states, qo_indptr, state_slots, KH, D, H, V, out)
-#define PICK(PF)                                                                                                             \
-    do {                                                                                                                     \
-        if (D <= 32) LAUNCH(2, PF); else if (D <= 64) LAUNCH(4, PF); else if (D <= 128) LAUNCH(8, PF);                       \
-        else if (D <= 256) LAUNCH(16, PF); else LAUNCH(32, PF);                                                              \
-    } while (0)
-    if (single_tokens) PICK(false); else PICK(true);
-#undef PICK
-#undef LAUNCH
-    return kb_launch_result();
+                                  float* out, int num_rows, int single_tokens, int channel_decay, cudaStream_t stream) {
+    if (channel_decay)
+        return launch_linear_recurrence<true, true>(qn, kn, vv, beta, decay, states, qo_indptr, state_slots, KH, D, H, V, out, num_rows, single_tokens, stream);
+    return launch_linear_recurrence<true, false>(qn, kn, vv, beta, decay, states, qo_indptr, state_slots, KH, D, H, V, out, num_rows, single_tokens, stream);
 }
 
-KB_EXPORT int kb_delta_gated_norm(const float* o, const void* proj, int stride, int gate_offset, int is_bf16, const float* w,
+KB_EXPORT int kb_delta_gated_norm(const float* o, const void* gate, int gate_stride, int sigmoid_gate, int is_bf16, const float* w,
                                   float eps, int H, int V, void* out, int T, cudaStream_t stream) {
     if (T == 0) return 0;
-    if (!o || !proj || !w || !out) return KB_ERR_NULL;
+    if (!o || !gate || !w || !out) return KB_ERR_NULL;
     if (is_bf16)
-        kb_launch(delta_gated_norm_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream, o, (const __nv_bfloat16*)proj, stride, gate_offset, w, eps, H, V, (__nv_bfloat16*)out);
+        kb_launch(delta_gated_norm_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream, o, (const __nv_bfloat16*)gate, gate_stride, sigmoid_gate, w, eps, H, V, (__nv_bfloat16*)out);
     else
-        kb_launch(delta_gated_norm_kernel<float>, dim3(T), dim3(128), 0, stream, o, (const float*)proj, stride, gate_offset, w, eps, H, V, (float*)out);
+        kb_launch(delta_gated_norm_kernel<float>, dim3(T), dim3(128), 0, stream, o, (const float*)gate, gate_stride, sigmoid_gate, w, eps, H, V, (float*)out);
     return kb_launch_result();
 }

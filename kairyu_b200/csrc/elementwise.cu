@@ -442,3 +442,23 @@ KB_EXPORT int kb_gather_rows(const void* src, const int* rows, void* out, int is
         kb_launch(gather_rows_kernel<float>, dim3(R), dim3(256), 0, stream, (const float*)src, rows, (float*)out, H);
     return kb_launch_result();
 }
+
+// ------------------------------------------------------------------ weighted sum of two tensors
+// out = sa * a + sb * b, formed in 32-bit with one rounding (two mixers that run side by side on one input).
+template <typename T>
+__global__ void scaled_sum_kernel(const T* __restrict__ a, float sa, const T* __restrict__ b, float sb, T* __restrict__ out, size_t n) {
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = from_float<T>(fmaf(sa, to_float(a[i]), sb * to_float(b[i])));
+}
+
+KB_EXPORT int kb_scaled_sum(const void* a, float sa, const void* b, float sb, void* out, int is_bf16, long long n, cudaStream_t stream) {
+    if (n == 0) return 0;
+    if (!a || !b || !out) return KB_ERR_NULL;
+    const dim3 grid((unsigned)((n + 255) / 256));
+    if (is_bf16)
+        kb_launch(scaled_sum_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)a, sa, (const __nv_bfloat16*)b, sb, (__nv_bfloat16*)out, (size_t)n);
+    else
+        kb_launch(scaled_sum_kernel<float>, grid, dim3(256), 0, stream, (const float*)a, sa, (const float*)b, sb, (float*)out, (size_t)n);
+    return kb_launch_result();
+}

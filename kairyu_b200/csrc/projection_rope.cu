@@ -19,9 +19,9 @@
 template <typename T, typename TW>
 __global__ void __launch_bounds__(PR_THREADS)
 projection_norm_rope_write_kernel(T* __restrict__ packed, int stride, int k_offset, int v_offset, int Hq, int Hkv, int D, int DV,
-                                  const TW* __restrict__ wq, const TW* __restrict__ wk, float eps,
+                                  const TW* __restrict__ wq, const TW* __restrict__ wk, float eps, int per_head,
                                   const float* __restrict__ cos_table, const float* __restrict__ sin_table, int rot_half, int max_pos,
-                                  int interleaved, const int* __restrict__ positions, const int* __restrict__ row_ids,
+                                  int interleaved, const float* __restrict__ v_cos, const float* __restrict__ v_sin, int v_rot_half, const int* __restrict__ positions, const int* __restrict__ row_ids,
                                   const int* __restrict__ block_table, int max_pages, const int* __restrict__ write_from,
                                   T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size, int num_pages, int num_rows,
                                   int* flag) {
@@ -30,7 +30,7 @@ projection_norm_rope_write_kernel(T* __restrict__ packed, int stride, int k_offs
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int row = row_ids[t];
-    const bool pos_ok = rot_half == 0 || (pos >= 0 && pos < max_pos);
+    const bool pos_ok = (rot_half == 0 && v_rot_half == 0) || (pos >= 0 && pos < max_pos);
     const float* cs = cos_table + (size_t)(pos_ok ? pos : 0) * rot_half;
     const float* sn = sin_table + (size_t)(pos_ok ? pos : 0) * rot_half;
     // where the token's key and value rows go (nullptr: nowhere)
@@ -61,35 +61,20 @@ projection_norm_rope_write_kernel(T* __restrict__ packed, int stride, int k_offs
     T* q = packed + (size_t)t * stride;
     T* k = q + k_offset;
     const T* v = q + v_offset;
-    float inv_q = 1.0f, inv_k = 1.0f;
-    if (wq) {
-        float sq = 0.0f, sk = 0.0f;
-        for (int i = threadIdx.x; i < Hq * D; i += blockDim.x) {
-            const float x = to_float(q[i]);
-            sq += x * x;
-        }
-        for (int i = threadIdx.x; i < Hkv * D; i += blockDim.x) {
-            const float x = to_float(k[i]);
-            sk += x * x;
-        }
-        inv_q = rsqrtf(block_sum(sq, scratch) / (float)(Hq * D) + eps);
-        inv_k = rsqrtf(block_sum(sk, scratch) / (float)(Hkv * D) + eps);
-    }
     // a head is rot_half pairs and D - 2 * rot_half single columns: D - rot_half units
     const int units = D - rot_half;
-    for (int u = threadIdx.x; u < (Hq + Hkv) * units; u += blockDim.x) {
-        const int head = u / units, i = u % units;
+    // one unit of head `head`: normed by inv and the weight at w_first + column, rotated, stored
+    auto unit = [&](int head, int i, float inv, int w_first) {
         const bool is_q = head < Hq;
         const int first = (is_q ? head : head - Hq) * D;
         const T* src = (is_q ? q : k) + first;
         const TW* w = is_q ? wq : wk;
-        const float inv = is_q ? inv_q : inv_k;
         T* dst = is_q ? q + first : (k_dst ? k_dst + first : nullptr);
         if (i < rot_half) {
             int a, b;
             rotary_pair(i, rot_half, interleaved, a, b);
-            const float x = to_float(src[a]) * inv * (w ? to_float(w[first + a]) : 1.0f);
-            const float y = to_float(src[b]) * inv * (w ? to_float(w[first + b]) : 1.0f);
+            const float x = to_float(src[a]) * inv * (w ? to_float(w[w_first + a]) : 1.0f);
+            const float y = to_float(src[b]) * inv * (w ? to_float(w[w_first + b]) : 1.0f);
             float rx, ry;
             rotate(x, y, cs[i], sn[i], rx, ry);
             if (dst) {
@@ -98,11 +83,92 @@ projection_norm_rope_write_kernel(T* __restrict__ packed, int stride, int k_offs
             }
         } else if (dst) {
             const int c = i + rot_half;
-            dst[c] = from_float<T>(to_float(src[c]) * inv * (w ? to_float(w[first + c]) : 1.0f));
+            dst[c] = from_float<T>(to_float(src[c]) * inv * (w ? to_float(w[w_first + c]) : 1.0f));
+        }
+    };
+    if (per_head) {
+        // statistics a head (the weights are D entries, shared by the heads): a warp takes a head at a time
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+        for (int head = warp; head < Hq + Hkv; head += warps) {
+            float inv = 1.0f;
+            if (wq) {
+                const T* src = head < Hq ? q + head * D : k + (head - Hq) * D;
+                float ss = 0.0f;
+                for (int i = lane; i < D; i += 32) {
+                    const float x = to_float(src[i]);
+                    ss += x * x;
+                }
+                inv = rsqrtf(warp_sum(ss) / (float)D + eps);  // the butterfly also orders these reads before the writes below
+            }
+            for (int i = lane; i < units; i += 32) unit(head, i, inv, 0);
+        }
+    } else {
+        float inv_q = 1.0f, inv_k = 1.0f;
+        if (wq) {
+            float sq = 0.0f, sk = 0.0f;
+            for (int i = threadIdx.x; i < Hq * D; i += blockDim.x) {
+                const float x = to_float(q[i]);
+                sq += x * x;
+            }
+            for (int i = threadIdx.x; i < Hkv * D; i += blockDim.x) {
+                const float x = to_float(k[i]);
+                sk += x * x;
+            }
+            inv_q = rsqrtf(block_sum(sq, scratch) / (float)(Hq * D) + eps);
+            inv_k = rsqrtf(block_sum(sk, scratch) / (float)(Hkv * D) + eps);
+        }
+        for (int u = threadIdx.x; u < (Hq + Hkv) * units; u += blockDim.x) {
+            const int head = u / units;
+            unit(head, u % units, head < Hq ? inv_q : inv_k, (head < Hq ? head : head - Hq) * D);
         }
     }
-    if (v_dst)
+    if (v_dst && v_rot_half > 0) {
+        // values turned by their position over their first 2 * v_rot_half columns, with a table of their own
+        const float* vc = v_cos + (size_t)(pos_ok ? pos : 0) * v_rot_half;
+        const float* vs = v_sin + (size_t)(pos_ok ? pos : 0) * v_rot_half;
+        const int v_units = DV - v_rot_half;
+        for (int u = threadIdx.x; u < Hkv * v_units; u += blockDim.x) {
+            const int first = (u / v_units) * DV, i = u % v_units;
+            if (i < v_rot_half) {
+                int a, b;
+                rotary_pair(i, v_rot_half, interleaved, a, b);
+                float rx, ry;
+                rotate(to_float(v[first + a]), to_float(v[first + b]), vc[i], vs[i], rx, ry);
+                v_dst[first + a] = from_float<T>(pos_ok ? rx : 0.0f);
+                v_dst[first + b] = from_float<T>(pos_ok ? ry : 0.0f);
+            } else {
+                v_dst[first + i + v_rot_half] = v[first + i + v_rot_half];
+            }
+        }
+    } else if (v_dst) {
         for (int i = threadIdx.x; i < Hkv * DV; i += blockDim.x) v_dst[i] = v[i];
+    }
+}
+
+// Heads of V columns turned in place by the token's position (inverse: by minus it) over their first
+// 2 * rot_half columns: what a mixer whose cached values were turned does to its result.  32-bit arithmetic.
+template <typename T>
+__global__ void __launch_bounds__(PR_THREADS)
+rotate_heads_kernel(T* __restrict__ x, int stride, int H, int V, const float* __restrict__ cos_table, const float* __restrict__ sin_table,
+                    int rot_half, int max_pos, int interleaved, int inverse, const int* __restrict__ positions, int* flag) {
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const bool pos_ok = pos >= 0 && pos < max_pos;
+    const float* cs = cos_table + (size_t)(pos_ok ? pos : 0) * rot_half;
+    const float* sn = sin_table + (size_t)(pos_ok ? pos : 0) * rot_half;
+    pdl_wait();
+    if (threadIdx.x == 0 && flag && !pos_ok) atomicOr(flag, KB_FLAG_BAD_POS);
+    T* row = x + (size_t)t * stride;
+    for (int u = threadIdx.x; u < H * rot_half; u += blockDim.x) {
+        const int first = (u / rot_half) * V, i = u % rot_half;
+        int a, b;
+        rotary_pair(i, rot_half, interleaved, a, b);
+        float rx, ry;
+        rotate(to_float(row[first + a]), to_float(row[first + b]), cs[i], inverse ? -sn[i] : sn[i], rx, ry);
+        row[first + a] = from_float<T>(pos_ok ? rx : 0.0f);
+        row[first + b] = from_float<T>(pos_ok ? ry : 0.0f);
+    }
 }
 
 // The same on bfloat16 rows whose heads, offsets and rotated parts are whole 16-byte groups: a thread takes eight
@@ -263,25 +329,29 @@ projection_norm_rope_write_vec_kernel(__nv_bfloat16* __restrict__ packed, int st
             *reinterpret_cast<Bf16x8*>(v_dst + i * 8) = *reinterpret_cast<const Bf16x8*>(v + i * 8);
 }
 
-// wq/wk null: no norm.  cos/sin null (rot_half 0): no rotation.  k_cache null: q only.
+// wq/wk null: no norm; per_head: statistics a head and weights of D entries, else over the whole projection.
+// cos/sin null (rot_half 0): no rotation.  v_cos/v_sin (v_rot_half > 0): the values turn too, by a table of their
+// own of the same number of positions.  k_cache null: q only.
 KB_EXPORT int kb_projection_norm_rope_write(void* packed, int stride, int is_bf16, int T, int k_offset, int v_offset, int Hq, int Hkv,
-                                            int D, int DV, const void* wq, const void* wk, int w_bf16, float eps,
+                                            int D, int DV, const void* wq, const void* wk, int w_bf16, float eps, int per_head,
                                             const float* cos_table, const float* sin_table, int rot_half, int max_pos, int interleaved,
+                                            const float* v_cos, const float* v_sin, int v_rot_half,
                                             const int* positions, const int* row_ids, const int* block_table, int max_pages,
                                             const int* write_from, void* k_cache, void* v_cache, int page_size, int num_pages,
                                             int num_rows, int* flag, cudaStream_t stream) {
     if (T == 0) return 0;
     if (!packed || !positions || !row_ids) return KB_ERR_NULL;
     if ((wq == nullptr) != (wk == nullptr)) return KB_ERR_BAD_ARG;
-    if (Hq < 1 || Hkv < 1 || D < 1 || DV < 1 || rot_half < 0 || 2 * rot_half > D) return KB_ERR_BAD_ARG;
+    if (Hq < 1 || Hkv < 0 || (Hkv == 0 && k_cache) || D < 1 || DV < 1 || rot_half < 0 || 2 * rot_half > D) return KB_ERR_BAD_ARG;  // no key heads: queries alone
     if (rot_half > 0 && (!cos_table || !sin_table || max_pos < 1)) return KB_ERR_NULL;
+    if (v_rot_half < 0 || 2 * v_rot_half > DV || (v_rot_half > 0 && (!v_cos || !v_sin || max_pos < 1))) return KB_ERR_BAD_ARG;
     if (k_cache && (!v_cache || !block_table || page_size < 1)) return KB_ERR_NULL;
 #define LAUNCH(TT, TW)                                                                                                              \
     kb_launch(projection_norm_rope_write_kernel<TT, TW>, dim3(T), dim3(PR_THREADS), 0, stream, (TT*)packed, stride, k_offset,         \
-              v_offset, Hq, Hkv, D, DV, (const TW*)wq, (const TW*)wk, eps, cos_table, sin_table, rot_half, max_pos, interleaved,     \
-              positions, row_ids, block_table, max_pages, write_from, (TT*)k_cache, (TT*)v_cache, page_size, num_pages, num_rows, flag)
+              v_offset, Hq, Hkv, D, DV, (const TW*)wq, (const TW*)wk, eps, per_head, cos_table, sin_table, rot_half, max_pos,       \
+              interleaved, v_cos, v_sin, v_rot_half, positions, row_ids, block_table, max_pages, write_from, (TT*)k_cache, (TT*)v_cache, page_size, num_pages, num_rows, flag)
     // whole 16-byte groups everywhere: heads, offsets, rows, the rotated part (split halves: each half) and the pages
-    const bool groups_of_eight = is_bf16 && D % 8 == 0 && DV % 8 == 0 && stride % 8 == 0 && k_offset % 8 == 0 && v_offset % 8 == 0 &&
+    const bool groups_of_eight = !per_head && v_rot_half == 0 && is_bf16 && D % 8 == 0 && DV % 8 == 0 && stride % 8 == 0 && k_offset % 8 == 0 && v_offset % 8 == 0 &&
                                  (interleaved ? rot_half % 4 == 0 : rot_half % 8 == 0) && (uintptr_t)packed % 16 == 0 &&
                                  (uintptr_t)k_cache % 16 == 0 && (uintptr_t)v_cache % 16 == 0 && (uintptr_t)wq % 16 == 0 &&
                                  (uintptr_t)wk % 16 == 0 && (uintptr_t)cos_table % 16 == 0 && (uintptr_t)sin_table % 16 == 0;
@@ -299,5 +369,19 @@ KB_EXPORT int kb_projection_norm_rope_write(void* packed, int stride, int is_bf1
     }
 #undef LAUNCH
 #undef LAUNCH_VEC
+    return kb_launch_result();
+}
+
+KB_EXPORT int kb_rotate_heads(void* x, int stride, int is_bf16, int T, int H, int V, const float* cos_table, const float* sin_table,
+                              int rot_half, int max_pos, int interleaved, int inverse, const int* positions, int* flag, cudaStream_t stream) {
+    if (T == 0 || rot_half == 0) return 0;
+    if (!x || !cos_table || !sin_table || !positions) return KB_ERR_NULL;
+    if (H < 1 || V < 1 || rot_half < 0 || 2 * rot_half > V || max_pos < 1) return KB_ERR_BAD_ARG;
+    if (is_bf16)
+        kb_launch(rotate_heads_kernel<__nv_bfloat16>, dim3(T), dim3(PR_THREADS), 0, stream, (__nv_bfloat16*)x, stride, H, V, cos_table, sin_table,
+                  rot_half, max_pos, interleaved, inverse, positions, flag);
+    else
+        kb_launch(rotate_heads_kernel<float>, dim3(T), dim3(PR_THREADS), 0, stream, (float*)x, stride, H, V, cos_table, sin_table, rot_half,
+                  max_pos, interleaved, inverse, positions, flag);
     return kb_launch_result();
 }

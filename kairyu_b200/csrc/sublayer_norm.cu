@@ -84,3 +84,65 @@ KB_EXPORT int kb_residual_copy(const float* x, void* copy, long long n, cudaStre
     kb_launch(residual_copy_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, (__nv_bfloat16*)copy, (size_t)n);
     return kb_launch_result();
 }
+
+// A norm on a sub-layer's output and the norm that reads the stream next, as one kernel:
+//
+//     x[t] += y[t] * rsqrt(mean(y[t]^2) + eps_y) * wy       (y null: nothing is added)
+//     out[r] = x[t] * rsqrt(mean(x[t]^2) + eps_x) * wx      (out null: the sum alone)
+//
+// for t = rows[r] (rows null: every row, and x is left updated; with rows x is not written: the listed rows'
+// results are all that is wanted).  Statistics, both weights and the sum are 32-bit; y and out have the
+// activation dtype.  One block per row; the row is kept in shared memory between the passes.
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(256)
+sandwich_norm_kernel(float* __restrict__ x, const TA* __restrict__ y, const TW* __restrict__ wy, float eps_y, const TW* __restrict__ wx,
+                     float eps_x, TA* __restrict__ out, const int* __restrict__ rows, int H) {
+    extern __shared__ float row[];
+    __shared__ float scratch[32];
+    pdl_trigger();
+    const int r = blockIdx.x;
+    const int t = rows ? rows[r] : r;
+    pdl_wait();
+    float* xr = x + (size_t)t * H;
+    float inv_y = 0.0f;
+    if (y) {
+        float ss = 0.0f;
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            const float v = to_float(y[(size_t)t * H + i]);
+            row[i] = v;
+            ss += v * v;
+        }
+        inv_y = rsqrtf(block_sum(ss, scratch) / (float)H + eps_y);
+    }
+    float sx = 0.0f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = xr[i];
+        if (y) {
+            v += row[i] * inv_y * to_float(wy[i]);
+            if (!rows) xr[i] = v;
+        }
+        row[i] = v;
+        sx += v * v;
+    }
+    if (!out) return;
+    const float inv_x = rsqrtf(block_sum(sx, scratch) / (float)H + eps_x);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)r * H + i] = from_float<TA>(row[i] * inv_x * to_float(wx[i]));
+}
+
+KB_EXPORT int kb_sandwich_norm(float* x, const void* y, const void* wy, float eps_y, const void* wx, float eps_x, void* out, int act_bf16,
+                               int w_bf16, const int* rows, int R, int H, cudaStream_t stream) {
+    if (R == 0) return 0;
+    if (!x || (y && !wy) || (out && !wx) || (!y && !out)) return KB_ERR_NULL;
+    if (H < 1 || H > 12000) return KB_ERR_UNSUPPORTED_SIZE;  // the row lives in 48 KB of shared memory
+    const size_t smem = (size_t)H * sizeof(float);
+#define LAUNCH(TA, TW)                                                                                                                  \
+    kb_launch(sandwich_norm_kernel<TA, TW>, dim3(R), dim3(256), smem, stream, x, (const TA*)y, (const TW*)wy, eps_y, (const TW*)wx, eps_x, \
+              (TA*)out, rows, H)
+    if (act_bf16) {
+        if (w_bf16) LAUNCH(__nv_bfloat16, __nv_bfloat16); else LAUNCH(__nv_bfloat16, float);
+    } else {
+        if (w_bf16) LAUNCH(float, __nv_bfloat16); else LAUNCH(float, float);
+    }
+#undef LAUNCH
+    return kb_launch_result();
+}

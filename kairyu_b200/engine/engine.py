@@ -23,7 +23,7 @@ from kairyu_b200.models.decoder import DecoderModel
 from kairyu_b200.registry import architecture_of
 from kairyu_b200.sampling.params import SamplingParams
 from kairyu_b200.sampling.sampler import Sampler, SamplingRow
-from kairyu_b200.weights.loading import load_into, read_config
+from kairyu_b200.weights.loading import load_into, read_config, read_config_with_shapes
 from kairyu_b200.weights.random_init import init_random
 
 
@@ -63,7 +63,7 @@ def build_model(config: Mapping[str, Any], *, dtype: str, device: str) -> tuple[
 
 def load_model(model_dir: str | Path, *, dtype: str, device: str) -> tuple[DecoderModel, Any]:
     """kairyu/models/loader.py:106-265: read config.json, build, bind tensors by name."""
-    model, model_config = build_model(read_config(model_dir), dtype=dtype, device=device)
+    model, model_config = build_model(read_config_with_shapes(model_dir), dtype=dtype, device=device)
     load_into(model, model_dir)
     return model, model_config
 

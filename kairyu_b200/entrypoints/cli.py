@@ -128,11 +128,11 @@ def _validate(args: argparse.Namespace) -> int:
     from kairyu_b200.engine.engine import build_model
     import fnmatch
 
-    from kairyu_b200.weights import CheckpointReader, WeightError, read_config
-    from kairyu_b200.weights.loading import IGNORED_TENSORS
+    from kairyu_b200.weights import CheckpointReader, WeightError
+    from kairyu_b200.weights.loading import IGNORED_TENSORS, read_config_with_shapes
 
     try:
-        config = read_config(args.model)
+        config = read_config_with_shapes(args.model)
         model, parsed = build_model(config, dtype="bfloat16", device="meta")
         reader = CheckpointReader(args.model)
         specs = model.tensor_specs()

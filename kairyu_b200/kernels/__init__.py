@@ -335,13 +335,18 @@ def projection_norm_rope_write(
     k_cache: Optional[torch.Tensor] = None,
     v_cache: Optional[torch.Tensor] = None,
     flag: Optional[torch.Tensor] = None,
+    per_head_norm: bool = False,
+    v_cos: Optional[torch.Tensor] = None,
+    v_sin: Optional[torch.Tensor] = None,
 ) -> None:
     """On the packed rows ``[q | ... k at k_offset ... v at v_offset ...]``: RMS norm of q over all its ``heads * dim``
-    columns at once and of k over all of its (if weights of those sizes are given), rotation of the first
+    columns at once and of k over all of its (if weights of those sizes are given; with ``per_head_norm`` the statistics
+    are a head's and the weights ``dim`` entries that the heads share), rotation of the first
     ``2 * cos.shape[1]`` columns of every head (pairs (i, i + half), or (2i, 2i + 1) when ``interleaved``), q back in place, k
-    into ``k_cache`` [pages, page, kv_heads, dim] and v into ``v_cache`` [pages, page, kv_heads, value_dim]."""
+    into ``k_cache`` [pages, page, kv_heads, dim] and v into ``v_cache`` [pages, page, kv_heads, value_dim]; with ``v_cos`` /
+    ``v_sin`` (tables of as many positions) the first ``2 * v_cos.shape[1]`` columns of every value head turn too."""
     what = "projection_norm_rope_write"
-    _need_cuda(what, packed, positions, row_ids, q_norm_weight, k_norm_weight, cos, sin, block_table, write_from, k_cache, v_cache, flag)
+    _need_cuda(what, packed, positions, row_ids, q_norm_weight, k_norm_weight, cos, sin, block_table, write_from, k_cache, v_cache, flag, v_cos, v_sin)
     _need_i32(what, positions, row_ids, block_table, write_from)
     q_size, k_size, v_size = num_q_heads * head_dim, num_kv_heads * head_dim, num_kv_heads * value_dim
     if packed.stride(1) != 1 or k_offset < q_size or k_offset + k_size > packed.shape[1] or v_offset < 0 or v_offset + v_size > packed.shape[1]:
@@ -353,11 +358,23 @@ def projection_norm_rope_write(
         max_pos, rot_half = cos.shape
         if 2 * rot_half > head_dim:
             raise KernelError(f"{what}: {2 * rot_half} rotated columns in a head of {head_dim}")
+    v_rot_half = 0
+    if v_cos is not None:
+        if v_sin is None or v_cos.shape != v_sin.shape or v_cos.dtype != torch.float32 or v_sin.dtype != torch.float32 or not (v_cos.is_contiguous() and v_sin.is_contiguous()):
+            raise KernelError(f"{what}: the values' cos and sin must be contiguous fp32 tables of one shape")
+        if cos is not None and v_cos.shape[0] != max_pos:
+            raise KernelError(f"{what}: the values' table must hold as many positions as the keys'")
+        max_pos, v_rot_half = v_cos.shape
+        if 2 * v_rot_half > value_dim:
+            raise KernelError(f"{what}: {2 * v_rot_half} rotated columns in a value head of {value_dim}")
     w_bf16 = 0
     if q_norm_weight is not None:
-        if k_norm_weight is None or q_norm_weight.dtype != k_norm_weight.dtype or q_norm_weight.numel() != q_size or k_norm_weight.numel() != k_size \
+        want_q, want_k = (head_dim, head_dim) if per_head_norm else (q_size, k_size)
+        if num_kv_heads == 0:  # queries alone: the key weight is not used
+            want_k = k_norm_weight.numel() if k_norm_weight is not None else 0
+        if k_norm_weight is None or q_norm_weight.dtype != k_norm_weight.dtype or q_norm_weight.numel() != want_q or k_norm_weight.numel() != want_k \
                 or not (q_norm_weight.is_contiguous() and k_norm_weight.is_contiguous()):
-            raise KernelError(f"{what}: q and k norm weights come together, in one dtype, one entry a projection column")
+            raise KernelError(f"{what}: q and k norm weights come together, in one dtype, one entry a projection column (a head's column with per_head_norm)")
         w_bf16 = _is_bf16(q_norm_weight, what)
     page_size = num_pages = max_pages = num_rows = 0
     if k_cache is not None:
@@ -370,12 +387,41 @@ def projection_norm_rope_write(
             raise KernelError(f"{what}: a cache write needs the block table")
         num_rows, max_pages = block_table.shape
     fn = _fn("projection_rope", "kb_projection_norm_rope_write",
-             [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int,
-              c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+             [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_int, c_void_p, c_void_p, c_int,
+              c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
     _check(fn(packed.data_ptr(), packed.stride(0), _is_bf16(packed, what), packed.shape[0], int(k_offset), int(v_offset), num_q_heads, num_kv_heads,
-              head_dim, value_dim, _ptr(q_norm_weight), _ptr(k_norm_weight), w_bf16, float(eps), _ptr(cos), _ptr(sin), rot_half, max_pos,
-              1 if interleaved else 0, positions.data_ptr(), row_ids.data_ptr(), _ptr(block_table), max_pages, _ptr(write_from), _ptr(k_cache),
+              head_dim, value_dim, _ptr(q_norm_weight), _ptr(k_norm_weight), w_bf16, float(eps), 1 if per_head_norm else 0, _ptr(cos), _ptr(sin),
+              rot_half, max_pos, 1 if interleaved else 0, _ptr(v_cos), _ptr(v_sin), v_rot_half, positions.data_ptr(), row_ids.data_ptr(), _ptr(block_table), max_pages, _ptr(write_from), _ptr(k_cache),
               _ptr(v_cache), page_size, num_pages, num_rows, _ptr(flag), _stream()), what)
+
+
+def rotate_heads(x: torch.Tensor, *, heads: int, head_dim: int, cos: torch.Tensor, sin: torch.Tensor, positions: torch.Tensor,
+                 interleaved: bool = False, inverse: bool = False, flag: Optional[torch.Tensor] = None) -> None:
+    """In place on ``x`` [tokens, heads * head_dim]: the first ``2 * cos.shape[1]`` columns of every head turn by the
+    token's position (``inverse``: by minus it), pairs (i, i + half) or (2i, 2i + 1) when ``interleaved``; 32-bit arithmetic."""
+    what = "rotate_heads"
+    _need_cuda(what, x, cos, sin, positions, flag)
+    _need_i32(what, positions)
+    if x.stride(1) != 1 or x.shape[1] < heads * head_dim or positions.numel() != x.shape[0]:
+        raise KernelError(f"{what}: rows of at least heads * head_dim columns with unit inner stride, a position a row")
+    if cos.shape != sin.shape or cos.dtype != torch.float32 or sin.dtype != torch.float32 or not (cos.is_contiguous() and sin.is_contiguous()):
+        raise KernelError(f"{what}: cos and sin must be contiguous fp32 tables of one shape")
+    max_pos, rot_half = cos.shape
+    if 2 * rot_half > head_dim:
+        raise KernelError(f"{what}: {2 * rot_half} rotated columns in a head of {head_dim}")
+    fn = _fn("projection_rope", "kb_rotate_heads",
+             [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(fn(x.data_ptr(), x.stride(0), _is_bf16(x, what), x.shape[0], heads, head_dim, cos.data_ptr(), sin.data_ptr(), rot_half, max_pos,
+              1 if interleaved else 0, 1 if inverse else 0, positions.data_ptr(), _ptr(flag), _stream()), what)
+
+
+def scaled_sum(a: torch.Tensor, scale_a: float, b: torch.Tensor, scale_b: float, out: torch.Tensor) -> None:
+    """``out = scale_a * a + scale_b * b``, formed in 32-bit with one rounding."""
+    _need_cuda("scaled_sum", a, b, out)
+    if a.shape != b.shape or a.shape != out.shape or a.dtype != b.dtype or a.dtype != out.dtype or not (a.is_contiguous() and b.is_contiguous() and out.is_contiguous()):
+        raise KernelError("scaled_sum: three contiguous tensors of one shape and dtype")
+    fn = _fn("elementwise", "kb_scaled_sum", [c_void_p, c_float, c_void_p, c_float, c_void_p, c_int, ctypes.c_longlong, c_void_p])
+    _check(fn(a.data_ptr(), float(scale_a), b.data_ptr(), float(scale_b), out.data_ptr(), _is_bf16(a, "scaled_sum"), a.numel(), _stream()), "scaled_sum")
 
 
 # ----------------------------------------------------------------------------- attention
@@ -1510,6 +1556,48 @@ def output_norm_add(residual: torch.Tensor, y, weight: torch.Tensor, eps: float,
     )
 
 
+@dataclass
+class PendingNormed:
+    """What a block that norms its sub-layers' outputs may leave for the norm that reads the stream next:
+    ``residual += rmsnorm(values) * weight`` is still to be done, and that norm's kernel does it on its way."""
+
+    values: torch.Tensor
+    weight: torch.Tensor
+    eps: float
+
+    @property
+    def shape(self) -> torch.Size:
+        return self.values.shape
+
+
+def sandwich_norm(residual: torch.Tensor, pending: Optional[PendingNormed], weight: Optional[torch.Tensor], eps: float,
+                  out: Optional[torch.Tensor], *, rows: Optional[torch.Tensor] = None) -> None:
+    """``residual += rmsnorm(pending.values) * pending.weight`` (when given), then ``out = rmsnorm(residual) * weight``
+    (when given), in one kernel.  With ``rows`` only the listed rows are produced and the residual is not written."""
+    what = "sandwich_norm"
+    y = pending.values if pending is not None else None
+    wy = pending.weight if pending is not None else None
+    _need_cuda(what, residual, y, wy, weight, out, rows)
+    _need_i32(what, rows)
+    T, H = residual.shape
+    R = rows.numel() if rows is not None else T
+    if residual.dtype != torch.float32 or not residual.is_contiguous():
+        raise KernelError(f"{what}: the residual must be contiguous fp32")
+    if y is not None and (y.shape != (T, H) or not y.is_contiguous() or wy.numel() != H or (out is not None and y.dtype != out.dtype)):
+        raise KernelError(f"{what}: the pending rows must have the residual's shape and the activation dtype, their weight its width")
+    if out is not None and (out.shape[1] != H or out.shape[0] < R or not out.is_contiguous() or weight is None or weight.numel() != H):
+        raise KernelError(f"{what}: the output or its weight does not fit")
+    if y is None and out is None:
+        return
+    weights = [w for w in (wy, weight) if w is not None]
+    if any(w.dtype != weights[0].dtype or not w.is_contiguous() for w in weights):
+        raise KernelError(f"{what}: contiguous weights of one dtype")
+    act = out if out is not None else y
+    fn = _fn("sublayer_norm", "kb_sandwich_norm", [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(residual.data_ptr(), _ptr(y), _ptr(wy), float(pending.eps) if pending is not None else 0.0, _ptr(weight), float(eps), _ptr(out),
+              _is_bf16(act, what), _is_bf16(weights[0], what), _ptr(rows), R, H, _stream()), what)
+
+
 def residual_copy(residual: torch.Tensor, copy: torch.Tensor) -> None:
     """copy = residual in bfloat16."""
     _need_cuda("residual_copy", residual, copy)
@@ -1642,29 +1730,35 @@ def delta_prepare(
     beta: torch.Tensor,
     decay: torch.Tensor,
     flag: Optional[torch.Tensor] = None,
+    channel_a: Optional[torch.Tensor] = None,
 ) -> None:
     """Convolution + silu of the packed q|k|v columns, unit norms of q and k, beta and the decay, all
     to fp32; then the step's last inputs become the requests' kept inputs (``conv_state``
-    [slots, taps - 1, channels] fp32)."""
-    _need_cuda("delta_prepare", packed, gates, taps, conv_state, row_ids, qo_indptr, state_slots, a_log, dt_bias, q, k, v, beta, decay, flag)
+    [slots, taps - 1, channels] fp32).  ``gates`` [tokens, 2 * heads]: beta's logits, then the decay's input a head
+    (``dt_bias`` and ``decay`` a head).  With ``channel_a`` [tokens, heads * dim] the decay is one number a head and
+    key channel: ``gates`` is then [tokens, heads], ``dt_bias`` [heads * dim] and ``decay`` [tokens, heads * dim]."""
+    _need_cuda("delta_prepare", packed, gates, taps, conv_state, row_ids, qo_indptr, state_slots, a_log, dt_bias, q, k, v, beta, decay, flag, channel_a)
     _need_i32("delta_prepare", row_ids, qo_indptr, state_slots)
     T = packed.shape[0]
     channels = 2 * kv_heads * dim + heads * vdim
     n = taps.shape[1]
-    for tensor in (gates, taps, a_log, dt_bias, q, k, v, beta, decay) + ((conv_state,) if conv_state is not None else ()):
+    for tensor in (gates, taps, a_log, dt_bias, q, k, v, beta, decay) + ((conv_state,) if conv_state is not None else ()) + ((channel_a,) if channel_a is not None else ()):
         if tensor.dtype != torch.float32 or not tensor.is_contiguous():
             raise KernelError("delta_prepare: everything but the packed projection is contiguous fp32")
-    if packed.stride(1) != 1 or packed.shape[1] < channels or taps.shape[0] != channels or gates.shape != (T, 2 * heads):
+    per = 1 if channel_a is None else dim  # decays a head
+    if packed.stride(1) != 1 or packed.shape[1] < channels or taps.shape[0] != channels or gates.shape != (T, (2 if channel_a is None else 1) * heads):
         raise KernelError("delta_prepare: the packed projection, the taps or the gates do not fit the sizes")
+    if (channel_a is not None and channel_a.shape != (T, heads * dim)) or dt_bias.numel() != heads * per or a_log.numel() != heads:
+        raise KernelError("delta_prepare: the decay's inputs do not fit the sizes")
     if conv_state is not None and tuple(conv_state.shape[1:]) != (n - 1, channels):
         raise KernelError("delta_prepare: the kept inputs must be [slots, taps - 1, channels]")
-    if q.numel() != T * kv_heads * dim or k.numel() != q.numel() or v.numel() != T * heads * vdim or beta.numel() != T * heads or decay.numel() != T * heads:
+    if q.numel() != T * kv_heads * dim or k.numel() != q.numel() or v.numel() != T * heads * vdim or beta.numel() != T * heads or decay.numel() != T * heads * per:
         raise KernelError("delta_prepare: an output does not fit")
     fn = _fn("delta_rule", "kb_delta_prepare",
-             [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+             [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
               c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p])
     _check(
-        fn(packed.data_ptr(), packed.stride(0), _is_bf16(packed, "delta_prepare"), gates.data_ptr(), taps.data_ptr(), n, _ptr(conv_state),
+        fn(packed.data_ptr(), packed.stride(0), _is_bf16(packed, "delta_prepare"), gates.data_ptr(), _ptr(channel_a), taps.data_ptr(), n, _ptr(conv_state),
            row_ids.data_ptr(), qo_indptr.data_ptr(), state_slots.data_ptr(), a_log.data_ptr(), dt_bias.data_ptr(), kv_heads, dim, heads,
            vdim, q.data_ptr(), k.data_ptr(), v.data_ptr(), beta.data_ptr(), decay.data_ptr(), qo_indptr.numel() - 1, T, _ptr(flag), _stream()),
         "delta_prepare",
@@ -1674,9 +1768,10 @@ def delta_prepare(
 
 def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, states: torch.Tensor,
                      out: torch.Tensor, *, qo_indptr: torch.Tensor, state_slots: torch.Tensor, kv_heads: int, dim: int, heads: int,
-                     vdim: int) -> None:
+                     vdim: int, channel_decay: bool = False) -> None:
     """Every row's tokens in order through S <- g S + k (beta (v - g S^T k))^T, o = S^T q; ``states``
-    [slots, heads, vdim, dim] fp32 (S column by column) is read and left updated."""
+    [slots, heads, vdim, dim] fp32 (S column by column) is read and left updated.  ``decay``: [tokens, heads], or
+    [tokens, heads * dim] with ``channel_decay``: one decay a key channel (g then scales the rows of S)."""
     _need_cuda("delta_recurrence", q, k, v, beta, decay, states, out, qo_indptr, state_slots)
     _need_i32("delta_recurrence", qo_indptr, state_slots)
     for tensor in (q, k, v, beta, decay, states, out):
@@ -1686,29 +1781,129 @@ def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: to
         raise KernelError("delta_recurrence: the state must be [slots, heads, vdim, dim] and the output as large as v")
     if dim > 512:
         raise KernelError(f"delta_recurrence: dim {dim} > 512 is not supported")
+    if decay.numel() != q.shape[0] * heads * (dim if channel_decay else 1):
+        raise KernelError("delta_recurrence: the decay is one number a token and head, or with channel_decay one a token, head and key channel")
+    channel = 1 if channel_decay else 0
     fn = _fn("delta_rule", "kb_delta_recurrence",
-             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p])
+             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
     rows = qo_indptr.numel() - 1
     _check(
         fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), beta.data_ptr(), decay.data_ptr(), states.data_ptr(), qo_indptr.data_ptr(),
-           state_slots.data_ptr(), kv_heads, dim, heads, vdim, out.data_ptr(), rows, 1 if q.shape[0] == rows else 0, _stream()),
+           state_slots.data_ptr(), kv_heads, dim, heads, vdim, out.data_ptr(), rows, 1 if q.shape[0] == rows else 0, channel, _stream()),
         "delta_recurrence",
     )
 
 
 def delta_gated_norm(o: torch.Tensor, packed: torch.Tensor, gate_offset: int, weight: torch.Tensor, eps: float, out: torch.Tensor, *,
-                     heads: int, vdim: int) -> None:
-    """out[t, h] = o[t, h] / rms(o[t, h]) * weight * silu(gate[t, h]); the gate is columns
-    [gate_offset, gate_offset + heads * vdim) of the packed projection."""
+                     heads: int, vdim: int, gate_activation: str = "silu") -> None:
+    """out[t, h] = o[t, h] / rms(o[t, h]) * weight * act(gate[t, h]); the gate is columns
+    [gate_offset, gate_offset + heads * vdim) of ``packed`` (the packed projection, or a tensor of the gate's
+    own); ``gate_activation``: ``silu`` or ``sigmoid``."""
     _need_cuda("delta_gated_norm", o, packed, weight, out)
     T = packed.shape[0]
+    if gate_activation not in ("silu", "sigmoid"):
+        raise KernelError(f"delta_gated_norm: unknown gate activation {gate_activation!r} (silu, sigmoid)")
     if o.dtype != torch.float32 or weight.dtype != torch.float32 or not o.is_contiguous() or not out.is_contiguous() or out.dtype != packed.dtype:
         raise KernelError("delta_gated_norm: o and the weight are fp32, the output has the projection's dtype")
     if out.shape != (T, heads * vdim) or o.numel() != T * heads * vdim or weight.numel() != vdim or gate_offset + heads * vdim > packed.shape[1] or packed.stride(1) != 1:
         raise KernelError("delta_gated_norm: shape mismatch")
     fn = _fn("delta_rule", "kb_delta_gated_norm", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_float, c_int, c_int, c_void_p, c_int, c_void_p])
-    _check(fn(o.data_ptr(), packed.data_ptr(), packed.stride(0), int(gate_offset), _is_bf16(packed, "delta_gated_norm"), weight.data_ptr(),
-              float(eps), heads, vdim, out.data_ptr(), T, _stream()), "delta_gated_norm")
+    _check(fn(o.data_ptr(), packed.data_ptr() + int(gate_offset) * packed.element_size(), packed.stride(0), 1 if gate_activation == "sigmoid" else 0,
+              _is_bf16(packed, "delta_gated_norm"), weight.data_ptr(), float(eps), heads, vdim, out.data_ptr(), T, _stream()), "delta_gated_norm")
+
+
+# ----------------------------------------------------------------------------- selective state-space mixer
+
+
+def ssm_prepare(
+    packed: torch.Tensor,
+    dt_raw: torch.Tensor,
+    taps: torch.Tensor,
+    conv_bias: Optional[torch.Tensor],
+    conv_state: Optional[torch.Tensor],
+    *,
+    row_ids: torch.Tensor,
+    qo_indptr: torch.Tensor,
+    state_slots: torch.Tensor,
+    a_log: torch.Tensor,
+    dt_bias: torch.Tensor,
+    groups: int,
+    state: int,
+    heads: int,
+    vdim: int,
+    x: torch.Tensor,
+    b: torch.Tensor,
+    c: torch.Tensor,
+    dt: torch.Tensor,
+    decay: torch.Tensor,
+    flag: Optional[torch.Tensor] = None,
+) -> None:
+    """Convolution (+ bias) + silu of the columns ``x | B | C`` of ``packed`` (a view that starts at x) to fp32;
+    ``dt = softplus(dt_raw + dt_bias)`` and ``decay = exp(-exp(a_log) * dt)`` a token and head; then the step's last
+    inputs become the requests' kept inputs (``conv_state`` [slots, taps - 1, channels] fp32)."""
+    what = "ssm_prepare"
+    _need_cuda(what, packed, dt_raw, taps, conv_bias, conv_state, row_ids, qo_indptr, state_slots, a_log, dt_bias, x, b, c, dt, decay, flag)
+    _need_i32(what, row_ids, qo_indptr, state_slots)
+    T = packed.shape[0]
+    channels = heads * vdim + 2 * groups * state
+    n = taps.shape[1]
+    for tensor in (dt_raw, taps, a_log, dt_bias, x, b, c, dt, decay) + tuple(t for t in (conv_state, conv_bias) if t is not None):
+        if tensor.dtype != torch.float32 or not tensor.is_contiguous():
+            raise KernelError(f"{what}: everything but the packed projection is contiguous fp32")
+    if packed.stride(1) != 1 or packed.shape[1] < channels or taps.shape[0] != channels or dt_raw.shape != (T, heads) or (conv_bias is not None and conv_bias.numel() != channels):
+        raise KernelError(f"{what}: the packed projection, the taps, the bias or the step sizes do not fit the sizes")
+    if conv_state is not None and tuple(conv_state.shape[1:]) != (n - 1, channels):
+        raise KernelError(f"{what}: the kept inputs must be [slots, taps - 1, channels]")
+    if x.numel() != T * heads * vdim or b.numel() != T * groups * state or c.numel() != b.numel() or dt.numel() != T * heads or decay.numel() != T * heads \
+            or a_log.numel() != heads or dt_bias.numel() != heads:
+        raise KernelError(f"{what}: an output or a per-head constant does not fit")
+    fn = _fn("ssm", "kb_ssm_prepare",
+             [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+              c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p])
+    _check(
+        fn(packed.data_ptr(), packed.stride(0), _is_bf16(packed, what), dt_raw.data_ptr(), taps.data_ptr(), _ptr(conv_bias), n, _ptr(conv_state),
+           row_ids.data_ptr(), qo_indptr.data_ptr(), state_slots.data_ptr(), a_log.data_ptr(), dt_bias.data_ptr(), groups, state, heads, vdim,
+           x.data_ptr(), b.data_ptr(), c.data_ptr(), dt.data_ptr(), decay.data_ptr(), qo_indptr.numel() - 1, T, _ptr(flag), _stream()),
+        what,
+        launches=2 if n > 1 else 1,
+    )
+
+
+def ssm_recurrence(c: torch.Tensor, b: torch.Tensor, x: torch.Tensor, dt: torch.Tensor, decay: torch.Tensor, states: torch.Tensor,
+                   out: torch.Tensor, *, qo_indptr: torch.Tensor, state_slots: torch.Tensor, groups: int, state: int, heads: int, vdim: int) -> None:
+    """Every row's tokens in order through S <- decay S + dt B x^T, y = S^T C; ``states`` [slots, heads, vdim, state]
+    fp32 (S column by column) is read and left updated."""
+    what = "ssm_recurrence"
+    _need_cuda(what, c, b, x, dt, decay, states, out, qo_indptr, state_slots)
+    _need_i32(what, qo_indptr, state_slots)
+    for tensor in (c, b, x, dt, decay, states, out):
+        if tensor.dtype != torch.float32 or not tensor.is_contiguous():
+            raise KernelError(f"{what}: contiguous fp32 tensors only")
+    if tuple(states.shape[1:]) != (heads, vdim, state) or out.numel() != x.numel() or state > 512:
+        raise KernelError(f"{what}: the state must be [slots, heads, vdim, state <= 512] and the output as large as x")
+    rows = qo_indptr.numel() - 1
+    fn = _fn("ssm", "kb_ssm_recurrence",
+             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(c.data_ptr(), b.data_ptr(), x.data_ptr(), dt.data_ptr(), decay.data_ptr(), states.data_ptr(), qo_indptr.data_ptr(), state_slots.data_ptr(),
+              groups, state, heads, vdim, out.data_ptr(), rows, 1 if x.shape[0] == rows else 0, _stream()), what)
+
+
+def ssm_gated_norm(y: torch.Tensor, x: torch.Tensor, skip: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, *,
+                   heads: int, vdim: int, norm_groups: int) -> None:
+    """``out = groupnorm((y + skip[h] * x) * silu(z)) * weight``: the RMS norm runs over ``norm_groups`` equal parts of a
+    token's ``heads * vdim`` columns, each by its own root mean square.  ``z`` may be a view of a wider row."""
+    what = "ssm_gated_norm"
+    _need_cuda(what, y, x, skip, z, weight, out)
+    T, inner = out.shape
+    for tensor in (y, x, skip, weight):
+        if tensor.dtype != torch.float32 or not tensor.is_contiguous():
+            raise KernelError(f"{what}: y, x, the skip weights and the norm weight are contiguous fp32")
+    if inner != heads * vdim or y.numel() != T * inner or x.numel() != T * inner or skip.numel() != heads or weight.numel() != inner or inner % norm_groups \
+            or z.shape != (T, inner) or z.stride(1) != 1 or z.dtype != out.dtype or not out.is_contiguous():
+        raise KernelError(f"{what}: shape mismatch")
+    fn = _fn("ssm", "kb_ssm_gated_norm", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_float, c_int, c_int, c_int, c_void_p, c_int, c_void_p])
+    _check(fn(y.data_ptr(), x.data_ptr(), skip.data_ptr(), z.data_ptr(), z.stride(0), _is_bf16(z, what), weight.data_ptr(), float(eps), heads, vdim,
+              norm_groups, out.data_ptr(), T, _stream()), what)
 
 
 # ----------------------------------------------------------------------------- mixture of experts

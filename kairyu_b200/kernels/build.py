@@ -46,6 +46,7 @@ LIBRARIES: dict[str, list[str]] = {
     "layernorm": [],
     "projection_rope": [],
     "delta_rule": [],
+    "ssm": [],
     "moe": [],
 }
 

@@ -2,7 +2,7 @@
 built-in parts; more can be registered from outside with the same decorators."""
 
 from kairyu_b200.parts import (  # noqa: F401  (registration)
-    attention, block, delta_rule, diff_attention, embedding, ffn, gated_attention, latent_attention, learned_positions, moe, norm, rope,
+    attention, block, delta_rule, diff_attention, embedding, ffn, gated_attention, latent_attention, learned_positions, moe, norm, rope, side_by_side, state_space,
 )
 from kairyu_b200.parts.base import (
     BLOCKS,

@@ -56,6 +56,9 @@ class LayerSpec:
     ffn: Optional[PartSpec]  # None: a layer without a feed-forward (for arrangements that take one)
     mixer_norm: PartSpec
     ffn_norm: Optional[PartSpec]
+    # norms on the sub-layers' OUTPUTS, for arrangements that norm on both sides of a sub-layer
+    mixer_post_norm: Optional[PartSpec] = None
+    ffn_post_norm: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)

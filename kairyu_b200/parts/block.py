@@ -186,3 +186,50 @@ class ParallelBlock(Block):
         if self.ffn is None:
             return residual, mixed
         return residual, kernels.PendingSums(mixed, self.ffn.forward(normed, ctx))
+
+
+@BLOCKS.register("sandwich_norm")
+class SandwichNormBlock(Block):
+    """``x += post1(mixer(pre1(x))); x += post2(ffn(pre2(x)))``: a norm before and a norm after each sub-layer.  A layer
+    may have no feed-forward.
+
+    The residual is fp32.  A sub-layer's output is handed on with its post-norm still to be applied
+    (``kernels.PendingNormed``), and the kernel of the norm that reads the stream next norms it, adds it to the
+    residual and norms the sum, so a sub-layer costs one norm kernel although it has two norms.  The norms must
+    offer ``pending`` and take what it returns as ``delta`` (``rmsnorm`` does)."""
+
+    graph_safe = True
+
+    def __init__(self, *, layer: LayerSpec, dtype: torch.dtype, device: str, shared: dict, **_: object) -> None:
+        context = dict(dtype=dtype, device=device, shared=shared)
+        if layer.mixer_post_norm is None or (layer.ffn is not None and (layer.ffn_norm is None or layer.ffn_post_norm is None)):
+            raise ValueError("this arrangement needs a norm before and a norm after each sub-layer")
+        self.mixer_norm = NORMS.build(layer.mixer_norm, **context)
+        self.mixer = MIXERS.build(layer.mixer, **context)
+        self.mixer_post_norm = NORMS.build(layer.mixer_post_norm, **context)
+        self.ffn_norm = NORMS.build(layer.ffn_norm, **context) if layer.ffn is not None else None
+        self.ffn = FEED_FORWARDS.build(layer.ffn, **context) if layer.ffn is not None else None
+        self.ffn_post_norm = NORMS.build(layer.ffn_post_norm, **context) if layer.ffn is not None else None
+        self._parts = tuple(part for part in (self.mixer_norm, self.mixer, self.mixer_post_norm, self.ffn_norm, self.ffn, self.ffn_post_norm)
+                            if part is not None)
+        for norm in (self.mixer_post_norm, self.ffn_post_norm):
+            if norm is not None and not hasattr(norm, "pending"):
+                raise ValueError("this arrangement needs output norms that offer pending (rmsnorm does)")
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return [spec for part in self._parts for spec in part.tensor_specs()]
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        for part in self._parts:
+            part.load(tensors)
+
+    def bytes_streamed(self) -> int:
+        return sum(part.bytes_streamed() for part in self._parts)
+
+    def forward(self, residual: torch.Tensor, delta, ctx: StepContext, cache: CacheView):
+        normed = self.mixer_norm.apply(residual, delta, ctx)
+        pending = self.mixer_post_norm.pending(self.mixer.forward(normed, ctx, cache))
+        if self.ffn is None:
+            return residual, pending
+        normed = self.ffn_norm.apply(residual, pending, ctx)
+        return residual, self.ffn_post_norm.pending(self.ffn.forward(normed, ctx))

@@ -1,6 +1,7 @@
 """SiLU-gated feed-forward (kairyu/models/layers.py:193-244):
 ``down(silu(gate(x)) * up(x))``.  gate and up are one matrix product over the
-row-concatenated weight (the reference runs them as two)."""
+row-concatenated weight (the reference runs them as two).  ``names``: the three tensors'
+names under ``prefix`` (gate, up, down) where a file calls them otherwise."""
 
 from __future__ import annotations
 
@@ -25,10 +26,12 @@ class SwiGLU(FeedForward):
         activation: str,
         dtype: torch.dtype,
         device: str,
+        names: tuple = ("gate_proj.weight", "up_proj.weight", "down_proj.weight"),
         **_: object,
     ) -> None:
         if activation != "silu":
             raise ValueError(f"gated feed-forward activation {activation!r} is not implemented (silu)")
+        self.names = tuple(names)
         self.prefix = prefix
         self.hidden_size = hidden_size
         self.intermediate_size = intermediate_size
@@ -38,18 +41,18 @@ class SwiGLU(FeedForward):
 
     def tensor_specs(self) -> list[TensorSpec]:
         p = self.prefix
+        gate, up, down = self.names
         return [
-            TensorSpec(f"{p}.gate_proj.weight", (self.intermediate_size, self.hidden_size)),
-            TensorSpec(f"{p}.up_proj.weight", (self.intermediate_size, self.hidden_size)),
-            TensorSpec(f"{p}.down_proj.weight", (self.hidden_size, self.intermediate_size)),
+            TensorSpec(f"{p}.{gate}", (self.intermediate_size, self.hidden_size)),
+            TensorSpec(f"{p}.{up}", (self.intermediate_size, self.hidden_size)),
+            TensorSpec(f"{p}.{down}", (self.hidden_size, self.intermediate_size)),
         ]
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         p = self.prefix
-        self.w_gate_up = torch.cat(
-            [tensors[f"{p}.gate_proj.weight"], tensors[f"{p}.up_proj.weight"]], dim=0
-        ).contiguous()
-        self.w_down = tensors[f"{p}.down_proj.weight"].contiguous()
+        gate, up, down = self.names
+        self.w_gate_up = torch.cat([tensors[f"{p}.{gate}"], tensors[f"{p}.{up}"]], dim=0).contiguous()
+        self.w_down = tensors[f"{p}.{down}"].contiguous()
 
     def bytes_streamed(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))

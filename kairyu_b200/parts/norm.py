@@ -14,24 +14,30 @@ from kairyu_b200.parts.base import NORMS, Norm, StepContext, TensorSpec
 class RMSNorm(Norm):
     """``y = x * rsqrt(mean(x^2) + eps) * (offset + weight)`` with fp32 statistics.  ``offset`` is 0 unless
     given; a file that stores its norm weights around zero names 1, and the sum is then formed once,
-    at loading, in 32-bit, and held so."""
+    at loading, in 32-bit, and held so.  ``scalar``: the weight is ONE number for all coordinates (a tensor
+    without dimensions); it is spread over the width once, at loading, in 32-bit."""
 
     graph_safe = True
 
-    def __init__(self, *, name: str, size: int, eps: float, dtype: torch.dtype, device: str, offset: float = 0.0, **_: object) -> None:
+    def __init__(self, *, name: str, size: int, eps: float, dtype: torch.dtype, device: str, offset: float = 0.0, scalar: bool = False,
+                 **_: object) -> None:
         self.name = name  # full tensor name of the weight
         self.size = size
         self.eps = float(eps)
         self.offset = float(offset)
+        self.scalar = bool(scalar)
         self.dtype = dtype
         self.device = device
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> list[TensorSpec]:
-        return [TensorSpec(self.name, (self.size,), role="vector", init="norm" if self.offset == 0.0 else "normal")]
+        shape = () if self.scalar else (self.size,)
+        return [TensorSpec(self.name, shape, role="vector", init="norm" if self.offset == 0.0 else "normal")]
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.weight = tensors[self.name].contiguous()
+        if self.scalar:
+            self.weight = self.weight.float().reshape(1).expand(self.size).contiguous()
         if self.offset != 0.0:
             self.weight = (self.weight.float() + self.offset).contiguous()
 
@@ -49,8 +55,16 @@ class RMSNorm(Norm):
         count = rows.numel() if rows is not None else residual.shape[0]
         # a subset of rows (the model's last norm, at the wanted places) has a buffer of its own
         out = ctx.workspace.buffer("norm.out" if rows is None else "norm.rows.out", count, self.size, self.dtype)
+        if isinstance(delta, kernels.PendingNormed):  # a normed sub-layer output still to be added: one kernel for both norms
+            kernels.sandwich_norm(residual, delta, self.weight, self.eps, out, rows=rows)
+            return out
         kernels.rmsnorm(residual, self.weight, self.eps, out, delta=delta, rows=rows)
         return out
+
+    def pending(self, y: torch.Tensor) -> "kernels.PendingNormed":
+        """For an arrangement that norms a sub-layer's OUTPUT: ``residual += norm(y)`` handed on undone, for the
+        norm that reads the stream next to do in its own kernel (``apply`` of this class takes it as ``delta``)."""
+        return kernels.PendingNormed(y, self.weight, self.eps)
 
     def add_normed(self, residual: torch.Tensor, y, ctx: StepContext) -> torch.Tensor:
         """For an arrangement that norms a sub-layer's OUTPUT: ``residual += norm(y)``.  Returns the

@@ -70,11 +70,15 @@ def rotary_tables(
 ) -> tuple[torch.Tensor, torch.Tensor]:
     """(cos, sin), each [max_positions, dim/2] fp32, on the CPU.  ``wide_angles``: frequencies theta^(-2i/dim) and
     angles position * frequency are formed in 64-bit and only cos and sin are rounded to 32-bit, so that an entry
-    is the correctly rounded value at every position (no scaling kinds)."""
+    is the correctly rounded value at every position (no scaling, or the llama3 or linear kind)."""
     if wide_angles:
-        if scaling is not None:
-            raise ValueError("wide angles come without frequency scaling")
+        if scaling is not None and scaling.kind not in ("llama3", "linear"):
+            raise ValueError("wide angles come without frequency scaling, or with the llama3 or the linear kind")
         inv_freq = theta ** (-torch.arange(0, dim, 2, dtype=torch.float64) / dim)
+        if scaling is not None and scaling.kind == "llama3":
+            inv_freq = _llama3_inv_freq(inv_freq, scaling)
+        elif scaling is not None:
+            inv_freq = inv_freq / scaling.factor
         freqs = torch.arange(max_positions, dtype=torch.float64)[:, None] * inv_freq[None, :]
         return freqs.cos().float().contiguous(), freqs.sin().float().contiguous()
     factor = 1.0
@@ -84,6 +88,8 @@ def rotary_tables(
         inv_freq = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.int64).to(torch.float32) / dim))
         if scaling is not None and scaling.kind == "llama3":
             inv_freq = _llama3_inv_freq(inv_freq, scaling)
+        elif scaling is not None and scaling.kind == "linear":  # every frequency divided by the factor: positions interpolated
+            inv_freq = inv_freq / scaling.factor
     positions = torch.arange(max_positions, dtype=torch.float32)
     freqs = positions[:, None] * inv_freq[None, :]
     return (freqs.cos() * factor).contiguous(), (freqs.sin() * factor).contiguous()

@@ -68,6 +68,9 @@ def _register_builtin() -> None:
     from kairyu_b200.models import mapalorn
 
     register_architecture("Mapalorn", mapalorn.parse_mapalorn, mapalorn.mapalorn_spec)
+    from kairyu_b200.models import tapasun
+
+    register_architecture("Tapasun", tapasun.parse_tapasun, tapasun.tapasun_spec)
 
 
 _register_builtin()

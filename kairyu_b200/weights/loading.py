@@ -70,6 +70,16 @@ def read_config(model_dir: str | Path) -> dict[str, Any]:
     return config
 
 
+def read_config_with_shapes(model_dir: str | Path) -> dict[str, Any]:
+    """``read_config`` plus, under ``tensor_shapes``, the shape of every tensor of the folder's checkpoint as its headers
+    give them (no tensor is read): a design may leave a size to the tensors' shapes (the rank of a two-step projection)."""
+    config = read_config(model_dir)
+    if "tensor_shapes" not in config:
+        reader = CheckpointReader(model_dir)
+        config["tensor_shapes"] = {name: list(reader.shape(name)) for name in reader.names()}
+    return config
+
+
 def held_dtype(spec: TensorSpec, stored_tag: str, compute: torch.dtype) -> torch.dtype:
     """The dtype a tensor is kept in: matrices and biases in the compute dtype,
     integer tables as int32, and a ``vector`` stored in 32-bit stays 32-bit."""
