@@ -1,0 +1,437 @@
+"""Tapasun on the GPU against the plain implementation in ``tapasun_plain.py``: every mechanism alone, whole prompts
+against token-by-token decoding, portions down to two tokens, unequal requests in one batch over a pool so small that
+pages and state slots are used again, keys made to stand out (far away, at page borders, beside the first tokens),
+long decoding, the new kernels one by one, and greedy generation through ``LLM.generate``."""
+
+import numpy as np
+import pytest
+import torch
+
+import tapasun_plain as plain
+import traces
+from tapasun_cases import CASES, attention, config, dense, layer, left, make_weights, mamba2, parallel, relative_error, right, write_model
+
+pytestmark = pytest.mark.gpu
+
+# rms of the logits' error over rms of the logits, per position
+FP32_BOUND = 1e-4
+BF16_BOUND = 5e-2
+LENGTHS = [70, 45, 101, 38, 64, 83, 9, 55, 2, 1]
+
+
+def expected_rows(cfg, weights, requests):
+    return {name: plain.forward(cfg, weights, tokens).numpy() for name, tokens in requests.items()}
+
+
+def make_runner(folder, dtype, *, page_size, num_pages, max_requests=4, decode_mode="eager", max_model_len=1024):
+    from kairyu_b200.cache import CacheLayout, CacheManager, CacheStorage
+    from kairyu_b200.engine.engine import load_model
+    from kairyu_b200.engine.runner import ModelRunner
+
+    model, _ = load_model(folder, dtype=dtype, device="cuda")
+    layout = CacheLayout.from_slot_specs(model.cache_slot_specs())
+    cache = CacheManager(layout, num_pages=num_pages, page_size=page_size, max_requests=max_requests)
+    storage = CacheStorage(layout, num_pages=num_pages, page_size=page_size, max_requests=max_requests, dtype=model.dtype, device="cuda")
+    return ModelRunner(model, cache, storage, max_model_len=max_model_len, decode_mode=decode_mode, max_graph_batch=max_requests,
+                       check_tables=True, debug_poison=True)
+
+
+def judge(result, expected, dtype, what=""):
+    """float32: every position within the bound.  bfloat16: the weights make the softmax pick single keys, so that faults
+    show; rounding to bfloat16 then costs a few per cent at a typical position and more where two keys are close.  A fault
+    moves the median position beyond the bound or many positions far beyond it, so the median is held to BF16_BOUND and
+    few positions may be far off."""
+    errors = np.array([relative_error(row, expected[name][position]) for (name, position), row in result.items()])
+    if str(dtype).endswith("float32"):
+        print(f"[tapasun] {what} float32: worst {errors.max():.3e} bound {FP32_BOUND:.1e}")
+        worst = [(key, e) for key, e in zip(result, errors) if not e < FP32_BOUND][:12]
+        assert errors.max() < FP32_BOUND, (what, errors.max(), worst)
+    else:
+        far = float((errors >= 3 * BF16_BOUND).mean())
+        print(f"[tapasun] {what} bfloat16: median {np.median(errors):.3e} worst {errors.max():.3e} far off {far:.3f} bound {BF16_BOUND:.1e}")
+        assert np.median(errors) < BF16_BOUND and far <= 0.10, (what, np.median(errors), far)
+
+
+@pytest.fixture(scope="module", params=list(CASES))
+def case(request, tmp_path_factory):
+    cfg, seed, page_size, ranks = CASES[request.param]
+    weights = make_weights(cfg, seed, ranks)
+    folder = write_model(cfg, weights, tmp_path_factory.mktemp(request.param))
+    requests = traces.make_requests(cfg["vocab"], LENGTHS, seed=seed + 100)
+    return dict(name=request.param, cfg=cfg, page_size=page_size, weights=weights, folder=folder, requests=requests,
+                expected=expected_rows(cfg, weights, requests))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("decode_mode", ["eager", "cuda_graph"])
+def test_every_cut_matches_plain(case, dtype, decode_mode):
+    """Whole prompts, tails decoded token by token, portions of changing size and mixed batches, one after the other on
+    one engine whose pool holds far less than all requests (pages and state slots change hands; pages that went back are
+    overwritten before the next step)."""
+    requests = case["requests"]
+    cuts = {
+        "whole": traces.trace_whole(requests),
+        "tail": traces.trace_decode_tail(requests, 32),
+        "chunks": traces.trace_chunks(requests),
+        "twos": traces.trace_chunks(requests, sizes=(2,)),
+        "mixed": traces.trace_mixed(requests, seed=5),
+    }
+    pool = max(traces.peak_tokens(steps) for steps in cuts.values()) // case["page_size"] + 1
+    total = sum(len(t) for t in requests.values())
+    assert pool * case["page_size"] < total
+    runner = make_runner(case["folder"], dtype, page_size=case["page_size"], num_pages=pool, decode_mode=decode_mode)
+    results = {}
+    for cut, steps in cuts.items():
+        results[cut] = traces.run_in_process(runner, steps)
+        assert len(results[cut]) == total
+        judge(results[cut], case["expected"], dtype, f"{case['name']} {decode_mode} {cut}")
+        assert runner.cache.live_requests == 0
+    if decode_mode == "cuda_graph":
+        assert runner.counters["graph_replays"] > 0
+    if dtype == "float32":
+        # no 32-bit sum depends on the batch or on where a prompt was cut
+        for cut in ("tail", "chunks", "twos", "mixed"):
+            different = [key for key, row in results["whole"].items() if not np.array_equal(row, results[cut][key])]
+            assert not different, (cut, different[:12])
+
+
+LLAMA3 = {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 128}
+MIXERS = {
+    "attention heads of 32": attention(4, 2, 32, 32, 0.25, 16, scaling=LLAMA3),            # tensor cores in bfloat16
+    "attention heads of 128": attention(2, 1, 128, 128, 0.1, 128, scaling=LLAMA3),
+    "attention heads of 64": attention(4, 1, 64, 64, 0.2, 32, base=2000.0),
+    "attention heads of 96": attention(6, 3, 96, 96, 0.15, 48, scaling={"factor": 2.0}),
+    "attention heads of 256": attention(2, 2, 256, 256, 0.08, 64),
+    "attention wider values": attention(3, 3, 16, 40, 0.4, 16),                            # 32-bit arithmetic in both modes
+    "attention narrower values": attention(6, 2, 48, 16, 0.2, 24),
+    "attention two columns turn": attention(2, 1, 10, 10, 0.5, 2),
+    "left with delta": parallel(left(4, 1, 32, 32, 0.25, 16, scaling={"factor": 2.0}), right(4, 4, 16, 16, 4)),
+    "left wide with few delta heads": parallel(left(2, 2, 64, 64, 0.12, 64), right(4, 1, 32, 8, 2), left_scale=0.3, right_scale=1.1),
+    "left of unequal widths": parallel(left(3, 1, 24, 20, 0.3, 12, base=300.0), right(2, 2, 8, 24, 3)),
+    "left odd with delta of dim 5": parallel(left(2, 2, 6, 10, 0.5, 2), right(3, 1, 5, 7, 1), left_scale=1.0, right_scale=1.0),
+    "delta wide": parallel(left(1, 1, 16, 16, 0.3, 8), right(2, 2, 128, 64, 4), left_scale=0.1, right_scale=1.0),
+    "delta dim 200": parallel(left(1, 1, 16, 16, 0.3, 8), right(2, 1, 200, 40, 3), left_scale=0.1, right_scale=1.0),
+    "delta dim 300": parallel(left(1, 1, 16, 16, 0.3, 8), right(1, 1, 300, 24, 2), left_scale=0.1, right_scale=1.0),
+    "state space": mamba2(4, 16, 32, 2, 2, 4),
+    "state space one group one part": mamba2(6, 8, 64, 1, 1, 3),
+    "state space wide state": mamba2(2, 32, 128, 2, 4, 2),
+    "state space odd": mamba2(3, 6, 5, 3, 9, 1),
+    "state space state 160": mamba2(2, 24, 160, 1, 2, 5),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kind", list(MIXERS))
+def test_one_mixer_alone(kind, dtype, tmp_path):
+    """A model of one layer without feed-forward, so that the mixer is all that mixes: a prompt of 230 tokens in one
+    step, then 90 tokens decoded one by one through a graph."""
+    cfg = config(40, 53, [layer(MIXERS[kind], None)], embedding_scale=1.7)
+    weights = make_weights(cfg, 7, (5, 6))
+    folder = write_model(cfg, weights, tmp_path / "m")
+    tokens = traces.make_requests(53, [320], seed=3)["r0"]
+    expected = {"r0": plain.forward(cfg, weights, tokens).numpy()}
+    steps = traces.trace_decode_tail({"r0": tokens}, 90)
+    runner = make_runner(folder, dtype, page_size=16, num_pages=24, decode_mode="cuda_graph")
+    result = traces.run_in_process(runner, steps)
+    judge(result, expected, dtype, f"{kind} alone")
+
+
+def _aligned(weights, prefix, m, perm):
+    """Queries made of the keys' weights, head by head, behind a permutation of the input's coordinates: a query whose input
+    is x scores high against the key whose input is x permuted, and not against its own."""
+    group = m["heads"] // m["kv_heads"]
+    k = weights[f"{prefix}.k"].view(m["kv_heads"], m["dim"], -1)
+    q = torch.zeros(m["heads"] * m["dim"], k.shape[-1])
+    q[:, perm] = k.repeat_interleave(group, dim=0).reshape(m["heads"] * m["dim"], -1)
+    weights[f"{prefix}.q"] = q
+    if f"{prefix}.k.norm" in weights:
+        weights[f"{prefix}.q.norm"] = weights[f"{prefix}.k.norm"].clone()
+
+
+def stand_out_model(kind, page):
+    """(config, weights, tokens, wanted positions, the query of the pair 600 apart and its key's position)."""
+    if kind == "attention":
+        layers = [layer(attention(4, 2, 32, 32, 0.3, 16, scaling={"factor": 4.0, "low": 1.0, "high": 4.0, "original": 256}), None)]
+    elif kind == "attention borrowed":
+        layers = [layer(attention(2, 1, 64, 64, 0.2, 32), None), layer(mamba2(2, 8, 8, 1, 1, 2), None),
+                  layer(attention(4, 1, 64, 64, 0.2, 32, kv_from=0), None)]
+    elif kind == "left":
+        layers = [layer(parallel(left(3, 1, 24, 20, 0.3, 12, scaling={"factor": 2.0}), right(2, 2, 8, 8, 2), left_scale=1.0, right_scale=0.2), None)]
+    else:
+        layers = [layer(parallel(left(2, 2, 128, 128, 0.1, 64), right(2, 2, 8, 8, 2), left_scale=1.0, right_scale=0.2), None)]
+    vocab, width = 80, 48
+    cfg = config(width, vocab, layers, embedding_scale=1.0)
+    weights = make_weights(cfg, 21, (4, 4))
+    gen = torch.Generator().manual_seed(5)
+    perm = torch.randperm(width, generator=gen)
+    for index, entry in enumerate(cfg["layers"]):
+        if entry["type"] == "attention" and entry["mixer"].get("kv_from") is None:
+            _aligned(weights, f"l{index}.mix", entry["mixer"], perm)
+        elif entry["type"] == "parallel":
+            _aligned(weights, f"l{index}.mix.left", entry["mixer"]["left"], perm)
+    if kind == "attention borrowed":  # the borrowing layer's queries are layer 0's: made of its keys' weights
+        weights["l2.mix.q"] = weights["l0.mix.q"].repeat(2, 1).clone()
+        weights["l2.mix.q.norm"] = weights["l0.mix.q.norm"].clone()
+    # rare tokens come in pairs: token 8 + i is token i seen through the permutation (its embedding is token i's, permuted)
+    weights["embed"][8:16] = weights["embed"][0:8][:, perm]
+    L = 700
+    tokens = torch.randint(16, vocab, (L,), generator=gen).tolist()
+    wanted = []
+    for index, distance in enumerate([0, 1, page - 1, page, page + 1, 600, None, None]):
+        at = 680 - 9 * index
+        key = at - distance if distance is not None else index - 6
+        if distance != 0:
+            tokens[at], tokens[key] = index, 8 + index
+        wanted.append(at)
+    wanted += [0, 1, 2, page - 1, page]
+    return cfg, weights, tokens, wanted, 680 - 9 * 5, 680 - 9 * 5 - 600
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kind", ["attention", "attention borrowed", "left", "left wide"])
+def test_keys_that_stand_out(kind, dtype, tmp_path):
+    """A 700-token prompt in which rare tokens come in pairs: a query whose token also stands at distance 0, 1, page - 1,
+    page, page + 1 or 600, or at the sequence's first two places, scores far above the hundreds of other keys (the
+    queries are made of the keys' weights), so a key that is lost, read from a wrong page or turned by a wrong angle moves
+    the logits by far more than rounding.  Whole, cut in the middle of a page with the tail decoded, and in small portions, on pages that
+    earlier requests have shuffled."""
+    page = 16
+    cfg, weights, tokens, wanted, far_query, far_key = stand_out_model(kind, page)
+    L, vocab = len(tokens), cfg["vocab"]
+    logits = plain.forward(cfg, weights, tokens).numpy()
+    folder = write_model(cfg, weights, tmp_path / "m")
+    runner = make_runner(folder, dtype, page_size=page, num_pages=2 * (L // page + 2), decode_mode="cuda_graph")
+    # two requests of unequal length first, ended in the other order, so that the long one gets shuffled pages
+    warm = traces.make_requests(vocab, [150, 90], seed=8)
+    traces.run_in_process(runner, [
+        {"step": 0, "entries": [{"id": "r0", "tokens": warm["r0"], "want": []}, {"id": "r1", "tokens": warm["r1"][:50], "want": []}], "end": ["r0"]},
+        {"step": 1, "entries": [{"id": "r1", "tokens": warm["r1"][50:], "want": []}], "end": ["r1"]},
+    ])
+    start = 613  # the middle of a page
+    cuts = {
+        "whole": [{"step": 0, "entries": [{"id": "far", "tokens": tokens, "want": wanted}], "end": ["far"]}],
+        "tail": [{"step": 0, "entries": [{"id": "far", "tokens": tokens[:start], "want": [w for w in wanted if w < start]}], "end": []}]
+                + [{"step": 1 + n, "entries": [{"id": "far", "tokens": [tokens[start + n]], "want": [0] if start + n in wanted else []}],
+                    "end": ["far"] if start + n == L - 1 else []} for n in range(L - start)],
+        "portions": None,
+    }
+    steps, at, turn = [], 0, 0
+    while at < L:
+        size = min((37, 2, 64, 5, 129)[turn % 5], L - at)
+        steps.append({"step": len(steps), "entries": [{"id": "far", "tokens": tokens[at : at + size], "want": [w - at for w in wanted if at <= w < at + size]}],
+                      "end": ["far"] if at + size == L else []})
+        at, turn = at + size, turn + 1
+    cuts["portions"] = steps
+    for cut, steps in cuts.items():
+        result = traces.run_in_process(runner, steps)
+        assert sorted(position for _, position in result) == sorted(wanted)
+        judge(result, {"far": logits}, dtype, f"{kind} stand-out {cut}")
+    # the pairs do stand out: without the far key the logits at its query differ by hundreds of times the float32 bound
+    # (by 0.75 and 1.3 of their size in the two models whose first layer is the attention under test)
+    lost = list(tokens)
+    lost[far_key] = 17
+    assert relative_error(plain.forward(cfg, weights, lost).numpy()[far_query], logits[far_query]) > 0.015
+
+
+def test_state_does_not_leak_between_requests(tmp_path):
+    """Two state slots, six requests one after the other in pairs: a slot's memories and kept inputs are zeroed when it
+    changes hands (both recurrent mixers and their convolutions)."""
+    cfg, seed, page_size, ranks = CASES["small_pages"]
+    weights = make_weights(cfg, seed, ranks)
+    folder = write_model(cfg, weights, tmp_path / "m")
+    requests = traces.make_requests(cfg["vocab"], [40, 33, 25, 47, 18, 29], seed=12)
+    expected = expected_rows(cfg, weights, requests)
+    runner = make_runner(folder, "float32", page_size=page_size, num_pages=40, max_requests=2)
+    result = traces.run_in_process(runner, traces.trace_mixed(requests, seed=2, max_live=2))
+    judge(result, expected, "float32", "two state slots")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_small_kernels(dtype):
+    """The two-norm kernel (a normed output added, the sum normed; on all rows and on listed rows), the per-head norm
+    with rotation of keys and of values and the page write, the turning back of heads, and the weighted sum."""
+    from kairyu_b200 import kernels
+
+    g = torch.Generator().manual_seed(4)
+    tokens, width = 37, 72
+    tolerance = 1e-5 if dtype == torch.float32 else 0.03
+    x = torch.randn(tokens, width, generator=g) * 3
+    y = (torch.randn(tokens, width, generator=g) * 5).to(dtype)
+    wy, wx = torch.full((width,), 0.7), torch.full((width,), 1.3)
+    residual = x.clone().cuda()
+    out = torch.empty(tokens, width, dtype=dtype, device="cuda")
+    kernels.sandwich_norm(residual, kernels.PendingNormed(y.cuda(), wy.cuda(), 1e-5), wx.cuda(), 1e-6, out)
+    total = x.double() + plain.unit_rms(y.double(), 1e-5) * 0.7
+    assert (residual.cpu().double() - total).abs().max() < 1e-5  # the sum is kept in 32-bit
+    assert (out.cpu().double() - plain.unit_rms(total, 1e-6) * 1.3).abs().max() < tolerance
+    rows = torch.tensor([5, 0, 36], dtype=torch.int32, device="cuda")
+    again, few = x.clone().cuda(), torch.empty(3, width, dtype=dtype, device="cuda")
+    kernels.sandwich_norm(again, kernels.PendingNormed(y.cuda(), wy.cuda(), 1e-5), wx.cuda(), 1e-6, few, rows=rows)
+    assert torch.equal(few, out[rows.long()]) and torch.equal(again.cpu(), x)  # listed rows: the residual is left alone
+    kernels.sandwich_norm(again, None, wx.cuda(), 1e-6, few, rows=rows)
+    assert (few.cpu().double() - plain.unit_rms(x.double()[rows.long().cpu()], 1e-6) * 1.3).abs().max() < tolerance
+
+    page = 8
+    block_table = torch.tensor([[3, 1, 7, 5, 2, -1], [4, 6, 8, -1, -1, -1]], dtype=torch.int32, device="cuda")
+    row_ids = torch.tensor([0] * 30 + [1] * 7, dtype=torch.int32, device="cuda")
+    where = torch.tensor(list(range(5, 35)) + list(range(11, 18)), dtype=torch.int32, device="cuda")
+    write_from = torch.tensor([8, 0], dtype=torch.int32, device="cuda")  # row 0 only reads its first page
+    for heads, kvh, dim, vdim, rot, normed in ((3, 1, 20, 12, 8, True), (3, 2, 32, 16, 16, True), (2, 1, 64, 24, 64, False), (4, 4, 16, 8, 8, False),
+                                               (5, 0, 12, 6, 4, True)):
+        k_off, v_off = heads * dim, heads * dim + kvh * dim
+        freqs = plain.frequencies({"base": 100.0, "dims": rot})
+        vfreqs = plain.frequencies({"base": 100.0, "dims": vdim})
+        tables = [(torch.arange(64, dtype=torch.float64)[:, None] * f[None, :]) for f in (freqs, vfreqs)]
+        cos, sin, vcos, vsin = (fn(t).float().cuda() for t in tables for fn in (torch.cos, torch.sin))
+        qw = (1 + 0.2 * torch.randn(dim, generator=g)).to(torch.bfloat16)
+        kw = (1 + 0.2 * torch.randn(dim, generator=g)).to(torch.bfloat16)
+        source = torch.randn(tokens, v_off + kvh * vdim + 3, generator=g).to(dtype)
+        packed = source.clone().cuda()
+        k_cache = torch.zeros(9, page, max(kvh, 1), dim, dtype=dtype, device="cuda")
+        v_cache = torch.zeros(9, page, max(kvh, 1), vdim, dtype=dtype, device="cuda")
+        writes = kvh > 0
+        kernels.projection_norm_rope_write(
+            packed, num_q_heads=heads, num_kv_heads=kvh, head_dim=dim, value_dim=vdim, k_offset=k_off, v_offset=v_off, positions=where, row_ids=row_ids,
+            q_norm_weight=qw.to(dtype).cuda() if normed else None, k_norm_weight=kw.to(dtype).cuda() if normed else None, eps=1e-5, cos=cos, sin=sin,
+            interleaved=True, block_table=block_table if writes else None, write_from=write_from if writes else None,
+            k_cache=k_cache if writes else None, v_cache=v_cache if writes else None, per_head_norm=True,
+            v_cos=vcos if writes and not normed else None, v_sin=vsin if writes and not normed else None)
+        s = source.double()
+        q_in, k_in = s[:, :k_off].view(tokens, heads, dim), s[:, k_off:v_off].view(tokens, kvh, dim)
+        if normed:
+            q_in, k_in = plain.unit_rms(q_in, 1e-5) * qw.double(), plain.unit_rms(k_in, 1e-5) * kw.double()
+        q_want = plain.turn(q_in, where.cpu(), freqs).reshape(tokens, -1)
+        k_want = plain.turn(k_in, where.cpu(), freqs).reshape(tokens, -1)
+        v_want = s[:, v_off : v_off + kvh * vdim].view(tokens, kvh, vdim)
+        if not normed:
+            v_want = plain.turn(v_want, where.cpu(), vfreqs)
+        v_want = v_want.reshape(tokens, -1)
+        assert (packed[:, :k_off].cpu().double() - q_want).abs().max() < tolerance
+        assert torch.equal(packed[:, k_off:].cpu(), source[:, k_off:])
+        for t in range(tokens if writes else 0):
+            position, row = int(where[t]), int(row_ids[t])
+            slot = (int(block_table[row, position // page]), position % page)
+            if position >= int(write_from[row]):
+                assert (k_cache[slot].flatten().cpu().double() - k_want[t]).abs().max() < tolerance
+                assert (v_cache[slot].flatten().cpu().double() - v_want[t]).abs().max() < tolerance
+            else:
+                assert not k_cache[slot].any() and not v_cache[slot].any()
+        # turning the heads back by the same positions undoes the values' turn
+        if writes and not normed:
+            turned = plain.turn(s[:, :kvh * vdim].view(tokens, kvh, vdim), where.cpu(), vfreqs).reshape(tokens, -1).to(dtype)
+            rows_gpu = torch.cat([turned, torch.zeros(tokens, 5, dtype=dtype)], dim=1).cuda()
+            kernels.rotate_heads(rows_gpu, heads=kvh, head_dim=vdim, cos=vcos, sin=vsin, positions=where, interleaved=True, inverse=True)
+            assert (rows_gpu[:, : kvh * vdim].cpu().double() - s[:, : kvh * vdim]).abs().max() < 2 * tolerance
+            assert not rows_gpu[:, kvh * vdim :].any()
+
+    a = torch.randn(tokens, width, generator=g).to(dtype)
+    b = torch.randn(tokens, width, generator=g).to(dtype)
+    out = torch.empty(tokens, width, dtype=dtype, device="cuda")
+    kernels.scaled_sum(a.cuda(), 0.6, b.cuda(), -1.5, out)
+    assert (out.cpu().double() - (0.6 * a.double() - 1.5 * b.double())).abs().max() < tolerance
+
+
+@pytest.mark.parametrize("sizes", [
+    # heads, query/key heads, dim, vdim, channel decay, delta
+    (4, 2, 32, 16, True, True), (2, 2, 128, 64, True, True), (3, 1, 5, 7, True, True), (2, 1, 200, 24, True, True), (1, 1, 300, 40, True, True),
+    (4, 2, 32, 16, False, True), (4, 2, 16, 8, False, False), (2, 1, 160, 24, False, False), (3, 3, 5, 6, False, False),
+])
+def test_recurrence_kernel(sizes):
+    """The shared recurrence kernel in its three modes against the recurrence written out, on rows of unequal lengths in
+    one launch (a prompt of 70 tokens beside single tokens and a portion of two), starting from states that are not zero,
+    and again token by token: equal bits."""
+    from kairyu_b200 import kernels
+
+    H, KH, D, V, channel, delta = sizes
+    g = torch.Generator().manual_seed(6)
+    lengths = [70, 1, 2, 1, 33]
+    T = sum(lengths)
+    q = torch.randn(T, KH, D, generator=g) * D ** -0.5
+    k = torch.nn.functional.normalize(torch.randn(T, KH, D, generator=g), dim=-1)
+    v = torch.randn(T, H, V, generator=g)
+    beta = torch.rand(T, H, generator=g)
+    decay = torch.rand(T, H, D, generator=g) * 0.6 + 0.4 if channel else torch.rand(T, H, generator=g) * 0.6 + 0.4
+    slots = [3, 0, 5, 1, 2]
+    states0 = torch.randn(6, H, V, D, generator=g) * 0.3
+    want = torch.zeros(T, H, V, dtype=torch.float64)
+    final = states0.double().clone()
+    t0 = 0
+    for row, length in enumerate(lengths):
+        for h in range(H):
+            S = final[slots[row], h].T.clone()  # [D, V]
+            for t in range(t0, t0 + length):
+                kk, qq = k[t, h // (H // KH)].double(), q[t, h // (H // KH)].double()
+                gate = decay[t, h].double()
+                S = (gate[:, None] if channel else gate) * S
+                u = beta[t, h].double() * (v[t, h].double() - (S.T @ kk if delta else 0.0))
+                S = S + torch.outer(kk, u)
+                want[t, h] = S.T @ qq
+            final[slots[row], h] = S.T
+        t0 += length
+    i32 = dict(dtype=torch.int32, device="cuda")
+    indptr = torch.tensor([0] + list(np.cumsum(lengths)), **i32)
+    flat = dict(q=q.reshape(T, -1).cuda(), k=k.reshape(T, -1).cuda(), v=v.reshape(T, -1).cuda(), beta=beta.cuda(), decay=decay.reshape(T, -1).cuda())
+
+    def run(states, indptr, slots_gpu, rows):
+        out = torch.zeros(rows.numel(), H * V, device="cuda")
+        args = [flat[name][rows].contiguous() for name in ("q", "k", "v", "beta", "decay")]
+        if delta:
+            kernels.delta_recurrence(*args, states, out, qo_indptr=indptr, state_slots=slots_gpu, kv_heads=KH, dim=D, heads=H, vdim=V, channel_decay=channel)
+        else:
+            kernels.ssm_recurrence(args[0], args[1], args[2], args[3], args[4], states, out, qo_indptr=indptr, state_slots=slots_gpu, groups=KH, state=D,
+                                   heads=H, vdim=V)
+        return out
+
+    states = states0.clone().cuda()
+    got = run(states, indptr, torch.tensor(slots, **i32), torch.arange(T, device="cuda"))
+    assert (got.cpu().double() - want.reshape(T, -1)).abs().max() < 2e-5 * max(1.0, want.abs().max().item())
+    assert (states.cpu().double() - final).abs().max() < 2e-5 * max(1.0, final.abs().max().item())
+    # token by token, every row's next token in one launch of single tokens
+    states_single = states0.clone().cuda()
+    starts = [0] + list(np.cumsum(lengths))[:-1]
+    got_single = torch.zeros_like(got)
+    for step in range(max(lengths)):
+        live = [row for row, length in enumerate(lengths) if step < length]
+        rows = torch.tensor([starts[row] + step for row in live], device="cuda")
+        out = run(states_single, torch.arange(len(live) + 1, **i32), torch.tensor([slots[row] for row in live], **i32), rows)
+        got_single[rows] = out
+    assert torch.equal(got_single, got) and torch.equal(states_single, states)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_engine(case, dtype):
+    """``LLM.generate`` with a token budget that cuts the prompts into portions and batches them with decoding requests;
+    greedy tokens against the plain model's own greedy continuation."""
+    from kairyu_b200.entrypoints.llm import LLM
+    from kairyu_b200.entrypoints.prompt import TokensPrompt
+    from kairyu_b200.sampling.params import SamplingParams
+
+    cfg, weights = case["cfg"], case["weights"]
+    prompts = [tokens for tokens in list(case["requests"].values())[:6]]
+    new = 12
+    llm = LLM(model=str(case["folder"]), dtype=dtype, num_pages=64 * 16 // case["page_size"], page_size=case["page_size"], max_num_batched_tokens=24,
+              max_num_seqs=4, max_model_len=256)
+    outputs = llm.generate([TokensPrompt(prompt_token_ids=tokens) for tokens in prompts],
+                           SamplingParams(temperature=0.0, max_tokens=new, ignore_eos=True), use_tqdm=False)
+    for tokens, output in zip(prompts, outputs):
+        got = list(output.outputs[0].token_ids)
+        assert len(got) == new
+        # teacher-forced: at every step the engine's choice is (nearly) the plain model's best given the engine's own history
+        logits = plain.forward(cfg, weights, list(tokens) + got).numpy()
+        close = []
+        for step, token in enumerate(got):
+            row = logits[len(tokens) - 1 + step]
+            close.append((row.max() - row[token]) / row.std())
+        if dtype == "float32":
+            assert max(close) <= 1e-4, close
+        else:  # bfloat16 may turn a close call: most steps agree
+            assert np.mean(np.array(close) <= 0.15) >= 0.8, close
+
+
+def test_trace_program(case, tmp_path):
+    """The same through ``bin/trace_run``: a pool for the trace's peak."""
+    steps = traces.trace_mixed(case["requests"], seed=9)
+    result = traces.run_program(case["folder"], tmp_path / "out", steps, dtype="float32", max_tokens=traces.peak_tokens(steps), vocab=case["cfg"]["vocab"],
+                                extra=["--page-size", str(case["page_size"])])
+    worst = max(relative_error(row, case["expected"][name][position]) for (name, position), row in result.items())
+    assert worst < FP32_BOUND
