@@ -624,7 +624,7 @@ def main() -> int:
     parser.add_argument("--prompt-len", type=int, default=None, help="another prompt length than the shape's (with --gen-len, within the context length)")
     parser.add_argument("--gen-len", type=int, default=None)
     parser.add_argument("--context-len", type=int, default=None, help="another context length than the shape's (longer prompts)")
-    parser.add_argument("--design", choices=["makilorn", "karesun", "mapalorn"], default=None,
+    parser.add_argument("--design", choices=["makilorn", "karesun", "mapalorn", "tapasun"], default=None,
                         help="instead of the default workload: this design's prefill and decode throughput at a few layer sizes beside the closest other model of equal size")
     args = parser.parse_args()
     if args.design is not None:

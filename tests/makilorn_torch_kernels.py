@@ -44,25 +44,31 @@ def heads_linear(x, weight, out):
     out.copy_(torch.einsum("thk,hnk->thn", x.float(), weight.float()).to(out.dtype))
 
 
-def delta_prepare(packed, gates, taps, conv_state, *, row_ids, qo_indptr, state_slots, a_log, dt_bias, kv_heads, dim, heads, vdim,
-                  q, k, v, beta, decay, flag=None):
+def _convolve(inputs_of_row, taps, conv_state, qo_indptr, state_slots, tokens, bias=None):
+    """Causal convolution of each row's portion, reaching into its kept inputs, which are then replaced."""
     n = taps.shape[1]
-    channels = 2 * kv_heads * dim + heads * vdim
-    tokens = packed.shape[0]
-    conv = torch.zeros(tokens, channels)
+    conv = torch.zeros(tokens, taps.shape[0])
     for row in range(qo_indptr.numel() - 1):
         t0, t1 = int(qo_indptr[row]), int(qo_indptr[row + 1])
         slot = int(state_slots[row])
-        inputs = packed[t0:t1, :channels].float()
+        inputs = inputs_of_row(t0, t1)
         if n > 1:
-            history = torch.cat([conv_state[slot], inputs], dim=0)  # the kept inputs, then the step's
+            history = torch.cat([conv_state[slot], inputs], dim=0)
             conv_state[slot] = history[-(n - 1) :]
         else:
             history = inputs
         for index in range(t1 - t0):
-            window = history[index : index + n]  # inputs at offsets -(n-1) .. 0 of this token
-            conv[t0 + index] = (window * taps.t()).sum(0)
-    act = conv / (1.0 + torch.exp(-conv))
+            conv[t0 + index] = (history[index : index + n] * taps.t()).sum(0)
+    if bias is not None:
+        conv = conv + bias
+    return conv / (1.0 + torch.exp(-conv))
+
+
+def delta_prepare(packed, gates, taps, conv_state, *, row_ids, qo_indptr, state_slots, a_log, dt_bias, kv_heads, dim, heads, vdim,
+                  q, k, v, beta, decay, flag=None, channel_a=None):
+    channels = 2 * kv_heads * dim + heads * vdim
+    tokens = packed.shape[0]
+    act = _convolve(lambda t0, t1: packed[t0:t1, :channels].float(), taps, conv_state, qo_indptr, state_slots, tokens)
     qk = kv_heads * dim
     qh = act[:, :qk].view(tokens, kv_heads, dim)
     kh = act[:, qk : 2 * qk].view(tokens, kv_heads, dim)
@@ -70,31 +76,41 @@ def delta_prepare(packed, gates, taps, conv_state, *, row_ids, qo_indptr, state_
     k.view(tokens, kv_heads, dim).copy_(kh * torch.rsqrt(kh.pow(2).sum(-1, keepdim=True) + 1e-6))
     v.view(tokens, heads * vdim).copy_(act[:, 2 * qk :])
     beta.copy_(torch.sigmoid(gates[:, :heads]))
-    decay.copy_(torch.exp(-torch.exp(a_log) * torch.nn.functional.softplus(gates[:, heads:] + dt_bias)))
+    if channel_a is None:
+        decay.copy_(torch.exp(-torch.exp(a_log) * torch.nn.functional.softplus(gates[:, heads:] + dt_bias)))
+    else:
+        rate = torch.exp(a_log).repeat_interleave(dim)
+        decay.copy_(torch.exp(-rate * torch.nn.functional.softplus(channel_a + dt_bias)))
 
 
-def delta_recurrence(q, k, v, beta, decay, states, out, *, qo_indptr, state_slots, kv_heads, dim, heads, vdim):
+def _recurrence(q, k, v, beta, decay, states, out, qo_indptr, state_slots, kv_heads, dim, heads, vdim, channel, delta):
     tokens = q.shape[0]
     q, k = q.view(tokens, kv_heads, dim), k.view(tokens, kv_heads, dim)
     v, out = v.view(tokens, heads, vdim), out.view(tokens, heads, vdim)
+    decay = decay.view(tokens, heads, dim) if channel else decay.view(tokens, heads)
     for row in range(qo_indptr.numel() - 1):
         slot = int(state_slots[row])
         for h in range(heads):
             S = states[slot, h].t().clone()  # stored column by column: [vdim, dim]
             for t in range(int(qo_indptr[row]), int(qo_indptr[row + 1])):
                 kt, qt = k[t, h // (heads // kv_heads)], q[t, h // (heads // kv_heads)]
-                S = decay[t, h] * S
-                u = beta[t, h] * (v[t, h] - S.t() @ kt)
+                S = decay[t, h][:, None] * S if channel else decay[t, h] * S
+                u = beta[t, h] * (v[t, h] - S.t() @ kt) if delta else beta[t, h] * v[t, h]
                 S = S + torch.outer(kt, u)
                 out[t, h] = S.t() @ qt
             states[slot, h] = S.t()
 
 
-def delta_gated_norm(o, packed, gate_offset, weight, eps, out, *, heads, vdim):
+def delta_recurrence(q, k, v, beta, decay, states, out, *, qo_indptr, state_slots, kv_heads, dim, heads, vdim, channel_decay=False):
+    _recurrence(q, k, v, beta, decay, states, out, qo_indptr, state_slots, kv_heads, dim, heads, vdim, channel_decay, True)
+
+
+def delta_gated_norm(o, packed, gate_offset, weight, eps, out, *, heads, vdim, gate_activation="silu"):
     tokens = packed.shape[0]
     o = o.view(tokens, heads, vdim)
     gate = packed[:, gate_offset : gate_offset + heads * vdim].float().view(tokens, heads, vdim)
-    normed = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * weight * (gate / (1.0 + torch.exp(-gate)))
+    factor = torch.sigmoid(gate) if gate_activation == "sigmoid" else gate * torch.sigmoid(gate)
+    normed = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * weight * factor
     out.copy_(normed.reshape(tokens, heads * vdim).to(out.dtype))
 
 

@@ -55,16 +55,18 @@ def _place(cache, block_table, write_from, row, position):
 
 def projection_norm_rope_write(packed, *, num_q_heads, num_kv_heads, head_dim, value_dim, k_offset, v_offset, positions, row_ids,
                                q_norm_weight=None, k_norm_weight=None, eps=0.0, cos=None, sin=None, interleaved=False, block_table=None,
-                               write_from=None, k_cache=None, v_cache=None, flag=None):
+                               write_from=None, k_cache=None, v_cache=None, flag=None, per_head_norm=False, v_cos=None, v_sin=None):
     q_size, k_size, v_size = num_q_heads * head_dim, num_kv_heads * head_dim, num_kv_heads * value_dim
     for t in range(packed.shape[0]):
         position, row = int(positions[t]), int(row_ids[t])
-        q = packed[t, :q_size].float()
-        k = packed[t, k_offset : k_offset + k_size].float()
-        if q_norm_weight is not None:
-            q = q * torch.rsqrt(q.pow(2).mean() + eps) * q_norm_weight.float()
-            k = k * torch.rsqrt(k.pow(2).mean() + eps) * k_norm_weight.float()
-        q, k = q.view(num_q_heads, head_dim).clone(), k.view(num_kv_heads, head_dim).clone()
+        q = packed[t, :q_size].float().view(num_q_heads, head_dim).clone()
+        k = packed[t, k_offset : k_offset + k_size].float().view(num_kv_heads, head_dim).clone()
+        if q_norm_weight is not None and per_head_norm:
+            q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_norm_weight.float()
+            k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_norm_weight.float()
+        elif q_norm_weight is not None:
+            q = (q.reshape(-1) * torch.rsqrt(q.pow(2).mean() + eps) * q_norm_weight.float()).view(num_q_heads, head_dim)
+            k = (k.reshape(-1) * torch.rsqrt(k.pow(2).mean() + eps) * k_norm_weight.float()).view(num_kv_heads, head_dim)
         if cos is not None:
             for h in range(num_q_heads):
                 q[h] = _turn(q[h], cos[position], sin[position], interleaved)
@@ -74,8 +76,12 @@ def projection_norm_rope_write(packed, *, num_q_heads, num_kv_heads, head_dim, v
         if k_cache is not None:
             place = _place(k_cache, block_table, write_from, row, position)
             if place is not None:
+                v = packed[t, v_offset : v_offset + v_size].float().view(num_kv_heads, value_dim).clone()
+                if v_cos is not None:
+                    for h in range(num_kv_heads):
+                        v[h] = _turn(v[h], v_cos[position], v_sin[position], interleaved)
                 k_cache[place[0], place[1]] = k.to(k_cache.dtype)
-                v_cache[place[0], place[1]] = packed[t, v_offset : v_offset + v_size].view(num_kv_heads, value_dim)
+                v_cache[place[0], place[1]] = v.to(v_cache.dtype)
 
 
 def latent_norm_write(packed, offset, rank, weight, eps, cache, *, positions, row_ids, block_table, write_from, flag=None, rot_dim=0,
