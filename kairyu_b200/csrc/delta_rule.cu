@@ -8,25 +8,20 @@
 // D^-1/2); beta = sigmoid(b), g = exp(-exp(A_log) * softplus(a + dt_bias)) per head.  Head h uses
 // q/k head h / (H / KH).  The output is o / rms(o) * w * silu(gate) per head.
 //
-// Four kernels:
+// With a decay a head AND key channel (g a row of D numbers, from a projection of its own) g scales the rows of S.
+// The gate of the output is silu or sigmoid of columns of the packed projection or of a tensor of its own.
+//
+// Kernels:
 //   delta_prepare     per token and head (a warp each): convolution (reaching into the request's kept
 //                     inputs for the taps that lie before the step's first token), silu, unit norms;
-//                     beta and g per token; all results 32-bit
-//   delta_conv_state  per request: the last (taps - 1) inputs of the step become the kept inputs
-//   delta_recurrence  per (request, head, 16 columns of S): walks the request's tokens in order.
-//                     Columns of S are independent of one another, so the grid spreads them: sixteen
-//                     lanes own a column (a lane holds D/16 of its entries in registers), the two
-//                     dot products of a token meet in one butterfly, and the next sixteen tokens'
-//                     rows are fetched while this chunk is walked.  A token is a chain of dependent
-//                     steps whatever the layout; fewer lanes a column mean fewer instructions a
-//                     token but fewer warps for an SM to switch between.  With a = S^T k
-//                     and b = S^T q of the OLD S:  u = beta (v - g a),  o = g b + (k.q) u,
-//                     S = g S + k u^T, which is the recurrence above with one pass over S for the
-//                     dots and one for the update
-//   delta_gated_norm  per token and head: o / sqrt(mean(o^2) + eps) * w * silu(gate)
+//                     beta and g per token (g a head, or a head and key channel); all results 32-bit
+//   conv_state        (linear_recurrence.cuh) per request: the last (taps - 1) inputs of the step become the kept inputs
+//   the recurrence    linear_recurrence.cuh, with the delta and either kind of decay: per (request, head, 16 columns
+//                     of S) it walks the request's tokens in order
+//   delta_gated_norm  per token and head: o / sqrt(mean(o^2) + eps) * w * act(gate)
 //
 // Every sum runs in an order that depends on the sizes alone, never on the batch or on how a
-// prompt was cut: tokens are staged in chunks of sixteen, but a chunk's edge changes no arithmetic.
+// prompt was cut.
 #include "common.cuh"
 #include "linear_recurrence.cuh"
 
