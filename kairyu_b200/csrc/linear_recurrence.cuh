@@ -10,7 +10,9 @@
 //   !CHANNEL: g is one number a token and head
 //
 // With a = S^T (g k) and b = S^T (g q) of the OLD S:  u = beta (v - a),  o = b + (k.q) u,  S = g S + k u^T,
-// which is the recurrence with one pass over S for the dots and one for the update.
+// which is the recurrence with one pass over S for the dots and one for the update.  Without the delta u does
+// not depend on S, the state's chain is one multiply-add a token, and the loop over tokens is unrolled so that the
+// read-outs' butterflies overlap.
 //
 // One block per (request, head, group of columns of S); columns are independent of one another, LANES lanes
 // own a column (a lane holds D/LANES of its entries in registers), the two dot products of a token meet in one
@@ -187,6 +189,25 @@ linear_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__
         }
         __syncthreads();
         const bool upper = (part & (LANES / 2)) != 0;
+        if constexpr (!DELTA) {
+            // Without the delta what is written does not depend on S: the state's chain is one multiply-add a token, and
+            // the read-outs' sums hang off it.  Four tokens are unrolled so that their butterflies are in flight together.
+#pragma unroll 4
+            for (int tt = 0; tt < nt; ++tt) {
+                const float g = gs[tt];
+                const float u = bs[tt] * vs[tt][local];
+                float b = 0.0f;
+#pragma unroll
+                for (int m = 0; m < DPT; ++m) {
+                    b = fmaf(S[m], qs[tt][m * LANES + part], b);
+                    S[m] = fmaf(ks[tt][m * LANES + part], u, g * S[m]);
+                }
+#pragma unroll
+                for (int offset = LANES / 2; offset > 0; offset >>= 1) b += __shfl_xor_sync(0xffffffffu, b, offset);
+                if (part == 0 && col < V) out[((size_t)(c0 + tt) * H + h) * V + col] = g * b + kqs[tt] * u;
+            }
+            continue;
+        }
         for (int tt = 0; tt < nt; ++tt) {
             float kv[DPT];
             float sg[CHANNEL ? DPT : 1];
@@ -211,7 +232,7 @@ linear_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__
             for (int offset = LANES / 4; offset > 0; offset >>= 1) z += __shfl_xor_sync(0xffffffffu, z, offset);
             a = __shfl_sync(0xffffffffu, z, lane & ~(LANES - 1));  // every lane needs a; b stays with the upper half
             const float g = CHANNEL ? 1.0f : gs[tt];
-            const float u = DELTA ? bs[tt] * (vs[tt][local] - g * a) : bs[tt] * vs[tt][local];
+            const float u = bs[tt] * (vs[tt][local] - g * a);
 #pragma unroll
             for (int m = 0; m < DPT; ++m) {
                 if constexpr (CHANNEL) S[m] = fmaf(kv[m], u, sg[m]);

@@ -15,6 +15,7 @@
 #include "rotary.cuh"
 
 #define PR_THREADS 256
+#define PR_MAX_HEADS 512  // heads of q and k together that the 16-byte kernel keeps per-head statistics for
 
 template <typename T, typename TW>
 __global__ void __launch_bounds__(PR_THREADS)
@@ -216,18 +217,20 @@ __device__ __forceinline__ Bf16x8 pack8(const float (&in)[8]) {
 template <typename TW>
 __global__ void __launch_bounds__(PR_THREADS)
 projection_norm_rope_write_vec_kernel(__nv_bfloat16* __restrict__ packed, int stride, int k_offset, int v_offset, int Hq, int Hkv, int D,
-                                      int DV, const TW* __restrict__ wq, const TW* __restrict__ wk, float eps,
+                                      int DV, const TW* __restrict__ wq, const TW* __restrict__ wk, float eps, int per_head,
                                       const float* __restrict__ cos_table, const float* __restrict__ sin_table, int rot_half, int max_pos,
-                                      int interleaved, const int* __restrict__ positions, const int* __restrict__ row_ids,
+                                      int interleaved, const float* __restrict__ v_cos, const float* __restrict__ v_sin, int v_rot_half,
+                                      const int* __restrict__ positions, const int* __restrict__ row_ids,
                                       const int* __restrict__ block_table, int max_pages, const int* __restrict__ write_from,
                                       __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int page_size,
                                       int num_pages, int num_rows, int* flag) {
     __shared__ float scratch[32];
+    __shared__ float head_inv[PR_MAX_HEADS];  // per_head: 1 / rms of every head of q, then of k
     pdl_trigger();
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int row = row_ids[t];
-    const bool pos_ok = rot_half == 0 || (pos >= 0 && pos < max_pos);
+    const bool pos_ok = (rot_half == 0 && v_rot_half == 0) || (pos >= 0 && pos < max_pos);
     const float* cs = cos_table + (size_t)(pos_ok ? pos : 0) * rot_half;
     const float* sn = sin_table + (size_t)(pos_ok ? pos : 0) * rot_half;
     __nv_bfloat16* k_dst = nullptr;
@@ -258,7 +261,23 @@ projection_norm_rope_write_vec_kernel(__nv_bfloat16* __restrict__ packed, int st
     __nv_bfloat16* k = q + k_offset;
     const __nv_bfloat16* v = q + v_offset;
     float inv_q = 1.0f, inv_k = 1.0f;
-    if (wq) {
+    if (wq && per_head) {
+        // statistics a head: a warp takes a head at a time, a lane eight columns a turn
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+        float x[8];
+        for (int head = warp; head < Hq + Hkv; head += warps) {
+            const __nv_bfloat16* src = head < Hq ? q + head * D : k + (head - Hq) * D;
+            float ss = 0.0f;
+            for (int i = lane; i < D / 8; i += 32) {
+                unpack8(*reinterpret_cast<const Bf16x8*>(src + i * 8), x);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) head_inv[head] = rsqrtf(ss / (float)D + eps);
+        }
+        __syncthreads();  // the statistics are read, and every head's columns were read before any is written
+    } else if (wq) {
         float sq = 0.0f, sk = 0.0f;
         float x[8];
         for (int i = threadIdx.x; i < Hq * D / 8; i += blockDim.x) {
@@ -284,12 +303,13 @@ projection_norm_rope_write_vec_kernel(__nv_bfloat16* __restrict__ packed, int st
         const int first = (is_q ? head : head - Hq) * D;
         const __nv_bfloat16* src = (is_q ? q : k) + first;
         const TW* w = is_q ? wq : wk;
-        const float inv = is_q ? inv_q : inv_k;
+        const float inv = (wq && per_head) ? head_inv[head] : (is_q ? inv_q : inv_k);
+        const int w_first = per_head ? 0 : first;  // per_head: the weights are a head's D entries
         __nv_bfloat16* dst = is_q ? q + first : (k_dst ? k_dst + first : nullptr);
         if (!dst) continue;
         float a[8], wa[8];
         unpack8(*reinterpret_cast<const Bf16x8*>(src + j * 8), a);
-        load_weights8(w, first + j * 8, inv, wa);
+        load_weights8(w, w_first + j * 8, inv, wa);
 #pragma unroll
         for (int e = 0; e < 8; ++e) a[e] *= wa[e];
         if (j >= rot_groups) {  // behind the rotated columns
@@ -309,7 +329,7 @@ projection_norm_rope_write_vec_kernel(__nv_bfloat16* __restrict__ packed, int st
         } else {
             float b[8], wb[8];
             unpack8(*reinterpret_cast<const Bf16x8*>(src + rot_half + j * 8), b);
-            load_weights8(w, first + rot_half + j * 8, inv, wb);
+            load_weights8(w, w_first + rot_half + j * 8, inv, wb);
             float c8[8], s8[8];
             load_floats(cs + j * 8, 8, c8);
             load_floats(sn + j * 8, 8, s8);
@@ -324,9 +344,33 @@ projection_norm_rope_write_vec_kernel(__nv_bfloat16* __restrict__ packed, int st
             *reinterpret_cast<Bf16x8*>(dst + rot_half + j * 8) = pack8(b);
         }
     }
-    if (v_dst)
+    if (v_dst && v_rot_half > 0) {
+        // interleaved pairs only (the launcher sends the split-halves layout to the scalar kernel): four pairs a group
+        const float* vc = v_cos + (size_t)(pos_ok ? pos : 0) * v_rot_half;
+        const float* vs = v_sin + (size_t)(pos_ok ? pos : 0) * v_rot_half;
+        const int v_groups = DV / 8, v_rot_groups = v_rot_half / 4;
+        for (int i = threadIdx.x; i < Hkv * v_groups; i += blockDim.x) {
+            const int j = i % v_groups;
+            float a[8];
+            unpack8(*reinterpret_cast<const Bf16x8*>(v + i * 8), a);
+            if (j < v_rot_groups) {
+                float c4[4], s4[4];
+                load_floats(vc + j * 4, 4, c4);
+                load_floats(vs + j * 4, 4, s4);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float rx, ry;
+                    rotate(a[2 * e], a[2 * e + 1], c4[e], s4[e], rx, ry);
+                    a[2 * e] = pos_ok ? rx : 0.0f;
+                    a[2 * e + 1] = pos_ok ? ry : 0.0f;
+                }
+            }
+            *reinterpret_cast<Bf16x8*>(v_dst + i * 8) = pack8(a);
+        }
+    } else if (v_dst) {
         for (int i = threadIdx.x; i < Hkv * DV / 8; i += blockDim.x)
             *reinterpret_cast<Bf16x8*>(v_dst + i * 8) = *reinterpret_cast<const Bf16x8*>(v + i * 8);
+    }
 }
 
 // wq/wk null: no norm; per_head: statistics a head and weights of D entries, else over the whole projection.
@@ -351,14 +395,14 @@ KB_EXPORT int kb_projection_norm_rope_write(void* packed, int stride, int is_bf1
               v_offset, Hq, Hkv, D, DV, (const TW*)wq, (const TW*)wk, eps, per_head, cos_table, sin_table, rot_half, max_pos,       \
               interleaved, v_cos, v_sin, v_rot_half, positions, row_ids, block_table, max_pages, write_from, (TT*)k_cache, (TT*)v_cache, page_size, num_pages, num_rows, flag)
     // whole 16-byte groups everywhere: heads, offsets, rows, the rotated part (split halves: each half) and the pages
-    const bool groups_of_eight = !per_head && v_rot_half == 0 && is_bf16 && D % 8 == 0 && DV % 8 == 0 && stride % 8 == 0 && k_offset % 8 == 0 && v_offset % 8 == 0 &&
+    const bool groups_of_eight = (!per_head || Hq + Hkv <= PR_MAX_HEADS) && (v_rot_half == 0 || (interleaved && v_rot_half % 4 == 0 && (uintptr_t)v_cos % 16 == 0 && (uintptr_t)v_sin % 16 == 0)) && is_bf16 && D % 8 == 0 && DV % 8 == 0 && stride % 8 == 0 && k_offset % 8 == 0 && v_offset % 8 == 0 &&
                                  (interleaved ? rot_half % 4 == 0 : rot_half % 8 == 0) && (uintptr_t)packed % 16 == 0 &&
                                  (uintptr_t)k_cache % 16 == 0 && (uintptr_t)v_cache % 16 == 0 && (uintptr_t)wq % 16 == 0 &&
                                  (uintptr_t)wk % 16 == 0 && (uintptr_t)cos_table % 16 == 0 && (uintptr_t)sin_table % 16 == 0;
 #define LAUNCH_VEC(TW)                                                                                                              \
     kb_launch(projection_norm_rope_write_vec_kernel<TW>, dim3(T), dim3(PR_THREADS), 0, stream, (__nv_bfloat16*)packed, stride,        \
-              k_offset, v_offset, Hq, Hkv, D, DV, (const TW*)wq, (const TW*)wk, eps, cos_table, sin_table, rot_half, max_pos,        \
-              interleaved, positions, row_ids, block_table, max_pages, write_from, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, \
+              k_offset, v_offset, Hq, Hkv, D, DV, (const TW*)wq, (const TW*)wk, eps, per_head, cos_table, sin_table, rot_half, max_pos, \
+              interleaved, v_cos, v_sin, v_rot_half, positions, row_ids, block_table, max_pages, write_from, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, \
               page_size, num_pages, num_rows, flag)
     if (groups_of_eight) {
         if (w_bf16) LAUNCH_VEC(__nv_bfloat16); else LAUNCH_VEC(float);

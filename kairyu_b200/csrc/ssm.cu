@@ -60,26 +60,24 @@ __global__ void __launch_bounds__(128)
 ssm_gated_norm_kernel(const float* __restrict__ y, const float* __restrict__ x, const float* __restrict__ skip,
                       const TA* __restrict__ z, int z_stride, const float* __restrict__ w, float eps, int H, int V, int parts,
                       TA* __restrict__ out) {
-    const int t = blockIdx.x;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    // one block per (token, part of the norm): the part's columns spread over the block's threads
+    __shared__ float scratch[32];
+    const int t = blockIdx.x, part = blockIdx.y;
     const int inner = H * V, size = inner / parts;
     pdl_wait();
     auto gated = [&](int e) -> float {
         const float value = y[(size_t)t * inner + e] + skip[e / V] * x[(size_t)t * inner + e];
         return value * silu_f(to_float(z[(size_t)t * z_stride + e]));
     };
-    for (int part = warp; part < parts; part += warps) {
-        float ss = 0.0f;
-        for (int e = lane; e < size; e += 32) {
-            const float v = gated(part * size + e);
-            ss += v * v;
-        }
-        ss = warp_sum(ss);
-        const float inv = rsqrtf(ss / (float)size + eps);
-        for (int e = lane; e < size; e += 32) {
-            const int c = part * size + e;
-            out[(size_t)t * inner + c] = from_float<TA>(gated(c) * inv * w[c]);
-        }
+    float ss = 0.0f;
+    for (int e = threadIdx.x; e < size; e += blockDim.x) {
+        const float v = gated(part * size + e);
+        ss += v * v;
+    }
+    const float inv = rsqrtf(block_sum(ss, scratch) / (float)size + eps);
+    for (int e = threadIdx.x; e < size; e += blockDim.x) {
+        const int c = part * size + e;
+        out[(size_t)t * inner + c] = from_float<TA>(gated(c) * inv * w[c]);
     }
 }
 
@@ -119,12 +117,12 @@ KB_EXPORT int kb_ssm_gated_norm(const float* y, const float* x, const float* ski
                                 float eps, int H, int V, int parts, void* out, int T, cudaStream_t stream) {
     if (T == 0) return 0;
     if (!y || !x || !skip || !z || !w || !out) return KB_ERR_NULL;
-    if (parts < 1 || (H * V) % parts != 0) return KB_ERR_BAD_ARG;
+    if (parts < 1 || parts > 65535 || (H * V) % parts != 0) return KB_ERR_BAD_ARG;
     if (is_bf16)
-        kb_launch(ssm_gated_norm_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream, y, x, skip, (const __nv_bfloat16*)z, z_stride, w, eps,
+        kb_launch(ssm_gated_norm_kernel<__nv_bfloat16>, dim3(T, parts), dim3(128), 0, stream, y, x, skip, (const __nv_bfloat16*)z, z_stride, w, eps,
                   H, V, parts, (__nv_bfloat16*)out);
     else
-        kb_launch(ssm_gated_norm_kernel<float>, dim3(T), dim3(128), 0, stream, y, x, skip, (const float*)z, z_stride, w, eps, H, V, parts,
+        kb_launch(ssm_gated_norm_kernel<float>, dim3(T, parts), dim3(128), 0, stream, y, x, skip, (const float*)z, z_stride, w, eps, H, V, parts,
                   (float*)out);
     return kb_launch_result();
 }
