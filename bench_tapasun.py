@@ -35,7 +35,7 @@ def tapasun_config(size: dict) -> dict:
     side = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
                      "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 2.0}}},
             "right": {"heads": heads, "kv_heads": heads // 2, "dim": 128, "vdim": 128, "conv": 4, "decay_rank": LOW_RANK, "gate_rank": LOW_RANK},
-            "left_scale": 0.6, "right_scale": 0.5}
+            "left_scale": 0.7, "right_scale": 0.4}
     space = {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 8, "norm_groups": 8, "conv": 4}
     mlp = {"kind": "dense", "ff": size["ff"]}
     mixers = [("attention", plain), ("attention", plain), ("parallel", side), ("mamba2", space),
