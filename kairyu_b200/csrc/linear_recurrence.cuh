@@ -208,7 +208,8 @@ linear_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__
             }
             continue;
         }
-        for (int tt = 0; tt < nt; ++tt) {
+#pragma unroll 4
+        for (int tt = 0; tt < nt; ++tt) {  // unrolled so that the next tokens' shared loads are issued ahead of this token's chain
             float kv[DPT];
             float sg[CHANNEL ? DPT : 1];
             float a = 0.0f, b = 0.0f;
