@@ -309,3 +309,21 @@ def test_generation_and_the_command_line_on_the_cpu(tmp_path, capsys, monkeypatc
         for _ in range(6):
             tokens.append(int(plain.forward(cfg, weights, tokens)[-1].argmax()))
         assert line["outputs"][0]["token_ids"] == tokens[len(prompt):]
+
+
+def test_bench_configurations_build():
+    """The sizes ``bench.py --design tapasun`` runs parse and build, and the dense decoder beside them is of equal size
+    (weights within a sixth of each other)."""
+    import math
+    import sys
+    from pathlib import Path
+
+    sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+    import bench_tapasun
+
+    for size in bench_tapasun.SIZES.values():
+        ours, _ = build_model(bench_tapasun.tapasun_config(size), dtype="bfloat16", device="meta")
+        dense_model, _ = build_model(bench_tapasun.dense_config(size), dtype="bfloat16", device="meta")
+        count = lambda model: sum(math.prod(spec.shape) for spec in model.tensor_specs())
+        assert 1.0 <= count(ours) / count(dense_model) < 7 / 6
+        assert ours.graph_safe() and len(ours.schedule) == bench_tapasun.LAYERS
