@@ -134,10 +134,11 @@ template <typename TA>
 __global__ void __launch_bounds__(128)
 delta_gated_norm_kernel(const float* __restrict__ o, const TA* __restrict__ gate, int gate_stride, int sigmoid_gate,
                         const float* __restrict__ w, float eps, int H, int V, TA* __restrict__ out) {
+    // a warp a (token, head); blockIdx.y spreads a token's heads over blocks, so that a step of few tokens still fills the device
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     pdl_wait();
-    for (int h = warp; h < H; h += warps) {
+    for (int h = blockIdx.y * warps + warp; h < H; h += gridDim.y * warps) {
         const float* oh = o + ((size_t)t * H + h) * V;
         float ss = 0.0f;
         for (int e = lane; e < V; e += 32) ss += oh[e] * oh[e];
@@ -193,9 +194,10 @@ KB_EXPORT int kb_delta_gated_norm(const float* o, const void* gate, int gate_str
                                   float eps, int H, int V, void* out, int T, cudaStream_t stream) {
     if (T == 0) return 0;
     if (!o || !gate || !w || !out) return KB_ERR_NULL;
+    if (H < 1 || H > 4 * 65535) return KB_ERR_UNSUPPORTED_SIZE;
     if (is_bf16)
-        kb_launch(delta_gated_norm_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream, o, (const __nv_bfloat16*)gate, gate_stride, sigmoid_gate, w, eps, H, V, (__nv_bfloat16*)out);
+        kb_launch(delta_gated_norm_kernel<__nv_bfloat16>, dim3(T, (H + 3) / 4), dim3(128), 0, stream, o, (const __nv_bfloat16*)gate, gate_stride, sigmoid_gate, w, eps, H, V, (__nv_bfloat16*)out);
     else
-        kb_launch(delta_gated_norm_kernel<float>, dim3(T), dim3(128), 0, stream, o, (const float*)gate, gate_stride, sigmoid_gate, w, eps, H, V, (float*)out);
+        kb_launch(delta_gated_norm_kernel<float>, dim3(T, (H + 3) / 4), dim3(128), 0, stream, o, (const float*)gate, gate_stride, sigmoid_gate, w, eps, H, V, (float*)out);
     return kb_launch_result();
 }

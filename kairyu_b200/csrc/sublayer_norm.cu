@@ -148,10 +148,13 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
     *reinterpret_cast<uint2*>(p) = raw;
 }
 
+// two_rows: shared memory holds the stream's row beside the output's, and both are fetched in the first pass, so that the
+// stream's row is not waited for behind the first reduction (a step of few rows is the latency of these passes).
 template <typename TA>
 __global__ void __launch_bounds__(256)
 sandwich_norm_vec_kernel(float* __restrict__ x, const TA* __restrict__ y, const float* __restrict__ wy, float eps_y,
-                         const float* __restrict__ wx, float eps_x, TA* __restrict__ out, const int* __restrict__ rows, int H) {
+                         const float* __restrict__ wx, float eps_x, TA* __restrict__ out, const int* __restrict__ rows, int H,
+                         int two_rows) {
     extern __shared__ __align__(16) float row[];
     __shared__ float scratch[32];
     pdl_trigger();
@@ -159,11 +162,13 @@ sandwich_norm_vec_kernel(float* __restrict__ x, const TA* __restrict__ y, const 
     const int t = rows ? rows[r] : r;
     pdl_wait();
     float* xr = x + (size_t)t * H;
+    float* kept = row + H;  // two_rows: the stream's row
     float inv_y = 0.0f;
     if (y) {
         float ss = 0.0f;
         for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
             const float4 v = load4(y + (size_t)t * H + i);
+            if (two_rows) store4(kept + i, load4(xr + i));
             store4(row + i, v);
             ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
         }
@@ -171,7 +176,7 @@ sandwich_norm_vec_kernel(float* __restrict__ x, const TA* __restrict__ y, const 
     }
     float sx = 0.0f;
     for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
-        float4 v = load4(xr + i);
+        float4 v = (y && two_rows) ? load4(kept + i) : load4(xr + i);
         if (y) {
             const float4 p = load4(row + i), w = load4(wy + i);
             v.x += p.x * inv_y * w.x; v.y += p.y * inv_y * w.y; v.z += p.z * inv_y * w.z; v.w += p.w * inv_y * w.w;
@@ -196,12 +201,14 @@ KB_EXPORT int kb_sandwich_norm(float* x, const void* y, const void* wy, float ep
     const size_t smem = (size_t)H * sizeof(float);
     const bool aligned = ((uintptr_t)x | (uintptr_t)y | (uintptr_t)wy | (uintptr_t)wx | (uintptr_t)out) % 16 == 0;
     if (H % 4 == 0 && !w_bf16 && aligned) {
+        const int two_rows = y && 2 * smem <= 48 * 1024;  // both rows fit the shared memory a block gets without asking
+        const size_t held = two_rows ? 2 * smem : smem;
         if (act_bf16)
-            kb_launch(sandwich_norm_vec_kernel<__nv_bfloat16>, dim3(R), dim3(256), smem, stream, x, (const __nv_bfloat16*)y, (const float*)wy, eps_y,
-                      (const float*)wx, eps_x, (__nv_bfloat16*)out, rows, H);
+            kb_launch(sandwich_norm_vec_kernel<__nv_bfloat16>, dim3(R), dim3(256), held, stream, x, (const __nv_bfloat16*)y, (const float*)wy, eps_y,
+                      (const float*)wx, eps_x, (__nv_bfloat16*)out, rows, H, two_rows);
         else
-            kb_launch(sandwich_norm_vec_kernel<float>, dim3(R), dim3(256), smem, stream, x, (const float*)y, (const float*)wy, eps_y, (const float*)wx,
-                      eps_x, (float*)out, rows, H);
+            kb_launch(sandwich_norm_vec_kernel<float>, dim3(R), dim3(256), held, stream, x, (const float*)y, (const float*)wy, eps_y, (const float*)wx,
+                      eps_x, (float*)out, rows, H, two_rows);
         return kb_launch_result();
     }
 #define LAUNCH(TA, TW)                                                                                                                  \
